@@ -1,0 +1,160 @@
+/*
+ * libmxdsa.so -- C ABI of the B200-native MXFP8 DeepSeek-Sparse-Attention library.
+ *
+ * Plain C: device pointers, sizes, strides, a CUDA stream handle.  No torch types.  Every entry
+ * point returns an mxdsa_status (0 = success) instead of throwing, exiting or trapping, and never
+ * synchronises the stream.  All pointers are DEVICE pointers unless stated otherwise.
+ *
+ * The reference project (dingirsu/MXDSA) has no extern "C" interface: its standalone library
+ * exports C++ launchers that take parameter structs by reference.  Each entry point below names
+ * the reference interface it stands in for (paths relative to the reference project).
+ *
+ * Packed operand format (reference tests/mxfp8_test_utils.py:30-104, csrc/attention/config.h:64-76)
+ *   Q row     : 528 bytes per (token, head): 512 E4M3 bytes, then 8 UE8M0 scale bytes (one per
+ *               pair of 32-wide chunks), then the same 8 bytes again.
+ *   prefill KV: one flat buffer, s_kv*512 data bytes followed by s_kv 16-byte scale slots
+ *               (8 UE8M0 bytes, one per 64 dims, stored twice).
+ *   decode KV : pages; each page is page_size*512 data bytes followed by page_size scale slots;
+ *               the page stride must be a multiple of 512 bytes.
+ *   V         : the same E4M3 bytes as K, scaled by the token's first scale byte and by the
+ *               per-dimension scale words w1 (dims 0-255) / w2 (dims 256-511): word j covers 32
+ *               dims and holds one UE8M0 byte four times.
+ */
+#ifndef MXDSA_H_
+#define MXDSA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MXDSA_HEADS 64        /* query heads per token                     */
+#define MXDSA_DIM 512         /* latent K/V width                          */
+#define MXDSA_ROW_BYTES 528   /* 512 data bytes + 16-byte scale slot       */
+#define MXDSA_SCHED_META_INTS 8
+
+typedef enum mxdsa_status {
+    MXDSA_OK = 0,
+    MXDSA_ERR_NULL = 1,          /* a required pointer is NULL                                  */
+    MXDSA_ERR_SHAPE = 2,         /* a size rule is violated (see the entry point)               */
+    MXDSA_ERR_ALIGN = 3,         /* a pointer or stride breaks an alignment rule                */
+    MXDSA_ERR_DEVICE = 4,        /* not a compute-capability 10.x device                        */
+    MXDSA_ERR_CUDA = 5,          /* a CUDA runtime/driver call failed; see mxdsa_last_cuda_error */
+    MXDSA_ERR_WORKSPACE = 6,     /* workspace missing or too small                              */
+    MXDSA_ERR_DEVICE_TIMEOUT = 7 /* a kernel gave up on a wait (reported by mxdsa_device_fault)  */
+} mxdsa_status;
+
+const char* mxdsa_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call made by this thread through the library. */
+int mxdsa_last_cuda_error(void);
+/* Synchronises `stream` and returns MXDSA_ERR_DEVICE_TIMEOUT if any kernel of this library on the
+ * current device abandoned a bounded wait since the last call, else MXDSA_OK.  For tests and
+ * debugging; the hot path never calls it. */
+int mxdsa_device_fault(void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Prefill.  Stands in for mxdsa::attention::run_dual_mxfp8_phase1_kernel<Prefill,512>
+ * (reference csrc/attention/launch.h:10-19, prefill_kernel.cuh:1039-1110) driven by
+ * MxFp8SparseAttnFwdParams (csrc/common/params.h:358-389), i.e. the device work behind
+ * dual_mxfp8_head64_sparse_prefill_fwd (csrc/bindings/binding.cpp:12-113).
+ *
+ * Query tokens 2p and 2p+1 share index row p.  Key j of row p is attended when
+ * 0 <= indices[p][j] < s_kv and j < topk_length[p] (topk when topk_length is NULL).
+ * Rules: s_q > 0 and even; topk > 0 and a multiple of 64; q, kv 16-byte aligned;
+ * stride_q_token a multiple of 16 bytes.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mxdsa_prefill_params {
+    int32_t s_q, s_kv, topk;
+    float sm_scale;
+    const void* q;               /* u8 [s_q][64][528]                                   */
+    int64_t stride_q_token;      /* bytes between query tokens (>= 64*528)              */
+    const void* kv;              /* u8 flat: s_kv*512 data bytes, then s_kv*16 slots    */
+    const int32_t* indices;      /* [s_q/2][topk]                                       */
+    int64_t stride_indices_pair; /* elements between index rows                         */
+    const float* attn_sink;      /* [64] or NULL                                        */
+    const int32_t* topk_length;  /* [s_q/2] or NULL                                     */
+    uint32_t w1[8], w2[8];
+    void* out;                   /* bf16 [s_q][64][512]                                 */
+    float* max_logits;           /* [s_q][64]  max of sm_scale*logit, -inf if no key    */
+    float* lse;                  /* [s_q][64]  natural-log sum-exp, +inf if no key      */
+    void* stream;                /* cudaStream_t                                        */
+} mxdsa_prefill_params;
+
+int mxdsa_prefill_fwd(const mxdsa_prefill_params* p);
+
+/* ------------------------------------------------------------------------------------------
+ * Decode.  num_sm_parts = max(SM count / s_q, 1), as the reference binding computes it
+ * (csrc/bindings/dual_mxfp8_sparse_decode.h:116).
+ * ------------------------------------------------------------------------------------------ */
+int mxdsa_num_sm_parts(int device, int s_q);
+
+/* Split-KV schedule.  Stands in for mxdsa::split_kv::run_get_decoding_sched_meta_kernel
+ * (reference csrc/split_kv/scheduler.cu:11-126, GetDecodeSchedMetaParams params.h:262-278).
+ * Produces, bit for bit, the reference's DecodingSchedMeta records (params.h:12-18):
+ *   sched_meta[i] = {begin_req, end_req (inclusive), begin_block, end_block (exclusive),
+ *                    begin_split, first_req_is_split, last_req_is_split, 0}
+ * for 64-key blocks over [main keys padded to 64 | extra keys], and num_splits[b+1] prefix sums. */
+typedef struct mxdsa_sched_params {
+    int32_t b, s_q, topk, extra_topk;   /* extra_topk = 0 when there is no extra cache */
+    const int32_t* topk_length;         /* [b] or NULL */
+    const int32_t* extra_topk_length;   /* [b] or NULL */
+    int32_t num_sm_parts;
+    int32_t* sched_meta;                /* out [num_sm_parts][8] */
+    int32_t* num_splits;                /* out [b+1]             */
+    void* stream;
+} mxdsa_sched_params;
+
+int mxdsa_decode_sched(const mxdsa_sched_params* p);
+
+/* Bytes of scratch that mxdsa_decode_fwd needs: fp32 partial outputs and base-2 LSEs for
+ * (b + num_sm_parts) splits, the shapes the reference allocates on every call
+ * (dual_mxfp8_sparse_decode.h:203-206). */
+size_t mxdsa_decode_workspace_bytes(int b, int s_q, int num_sm_parts);
+
+/* Decode attention + split combine.  Stands in for
+ * run_dual_mxfp8_phase1_kernel<DecodeWithSplitKV,512> (reference decode_kernel.cuh:989-1083,
+ * SparseAttnDualMxfp8DecodeParams params.h:198-238) followed by run_flash_mla_combine_kernel<bf16>
+ * (csrc/split_kv/combine.cu:415-448, CombineParams params.h:240-260).
+ *
+ * indices hold global slot ids (page * page_size + slot).  Queries 2p and 2p+1 of a request both
+ * follow index row p of that request, as in the reference (decode_kernel.cuh:108, 554-558).
+ * Key j is attended when indices[..][j] != -1 and j < topk_length[request].
+ * Rules: topk > 0 and a multiple of 64; page strides multiples of 512 bytes; extra_* all present
+ * or all absent (extra_topk_length optional); pointers 16-byte aligned. */
+typedef struct mxdsa_decode_params {
+    int32_t b, s_q, topk, extra_topk;
+    float sm_scale;
+    const void* q;                    /* u8 [b][s_q][64][528] */
+    int64_t stride_q_b, stride_q_s;   /* bytes                */
+    const void* kv;                   /* page pool            */
+    int32_t num_blocks, page_block_size;
+    int64_t stride_kv_block;          /* bytes, multiple of 512 */
+    const int32_t* indices;           /* [b][s_q][topk] */
+    int64_t stride_indices_b, stride_indices_s; /* elements */
+    const int32_t* topk_length;       /* [b] or NULL */
+    const float* attn_sink;           /* [64] or NULL */
+    const void* extra_kv;             /* or NULL */
+    int32_t extra_num_blocks, extra_page_block_size;
+    int64_t stride_extra_kv_block;
+    const int32_t* extra_indices;     /* [b][s_q][extra_topk] or NULL */
+    int64_t stride_extra_indices_b, stride_extra_indices_s;
+    const int32_t* extra_topk_length; /* [b] or NULL */
+    uint32_t w1[8], w2[8];
+    void* out;                        /* bf16 [b][s_q][64][512] */
+    float* lse;                       /* [b][s_q][64], natural log, without the sink term */
+    const int32_t* sched_meta;        /* [num_sm_parts][8] from mxdsa_decode_sched */
+    const int32_t* num_splits;        /* [b+1] */
+    int32_t num_sm_parts;
+    void* workspace;                  /* mxdsa_decode_workspace_bytes(...) bytes, 16-byte aligned */
+    size_t workspace_bytes;
+    void* stream;
+} mxdsa_decode_params;
+
+int mxdsa_decode_fwd(const mxdsa_decode_params* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXDSA_H_ */

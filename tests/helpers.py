@@ -1,0 +1,48 @@
+"""Shared helpers of the test-suite: golden loading and the north-star error measures."""
+import os
+
+import numpy as np
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# north-star tolerances against the reference kernel on identical inputs
+OUT_MAX_ABS = 2e-2
+OUT_MIN_COS = 0.9999
+LSE_MAX_ABS = 1e-3
+
+
+def bf16_bits_to_f32(u16: np.ndarray) -> np.ndarray:
+    return (np.asarray(u16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """fp32 values that are already exactly representable in bf16 -> their 16-bit patterns."""
+    return (np.asarray(x, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def load_golden(name: str):
+    return np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+
+
+def check_against_golden(g, out, lse, max_logits=None, lse_is_b_h_s=False, out_tol=OUT_MAX_ABS):
+    """Compare a full result (out [..,64,512] fp32 holding bf16 values) with a golden fixture."""
+    from oracle import mxdsa_oracle as O
+    rows = np.asarray(out, dtype=np.float32).reshape(-1, 512)
+    kept = rows[g["out_kept"]]
+    ref = bf16_bits_to_f32(g["out_rows"])
+    assert O.max_abs(kept, ref) <= out_tol, ("out max-abs", O.max_abs(kept, ref))
+    assert O.cosine(kept, ref) >= OUT_MIN_COS, ("out cosine", O.cosine(kept, ref))
+    # every row, through its sum over the 512 dims (bf16 rounding of 512 values of size ~|ref|)
+    sums = rows.astype(np.float64).sum(-1)
+    tol = 512 * out_tol * 0.25 + 1e-3 * g["out_abs"]
+    assert np.all(np.abs(sums - g["out_sum"]) <= tol), ("row sums", np.abs(sums - g["out_sum"]).max())
+    glse = g["lse"].transpose(0, 2, 1) if lse_is_b_h_s else g["lse"]
+    lse = np.asarray(lse)
+    assert np.array_equal(np.isposinf(lse), np.isposinf(glse)), "lse +inf pattern"
+    fin = np.isfinite(glse)
+    assert np.abs(lse[fin] - glse[fin]).max(initial=0.0) <= LSE_MAX_ABS
+    if max_logits is not None:
+        gm = g["max_logits"]
+        assert np.array_equal(np.isneginf(max_logits), np.isneginf(gm)), "max_logits -inf pattern"
+        fin = np.isfinite(gm)
+        assert np.abs(max_logits[fin] - gm[fin]).max(initial=0.0) <= LSE_MAX_ABS
