@@ -1,0 +1,86 @@
+"""ctypes view of libmxdsa.so (the C ABI declared in include/mxdsa.h).
+
+Raw device pointers in, status codes out.  The library is built in-tree by ``mxdsa_b200.build``;
+if it is missing this module raises -- there is no fallback implementation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libmxdsa.so")
+
+EXPORTS = (
+    "mxdsa_status_string", "mxdsa_last_cuda_error", "mxdsa_device_fault", "mxdsa_prefill_fwd",
+    "mxdsa_num_sm_parts", "mxdsa_decode_sched", "mxdsa_decode_workspace_bytes", "mxdsa_decode_fwd",
+)
+
+
+class PrefillParams(C.Structure):
+    _fields_ = [
+        ("s_q", C.c_int32), ("s_kv", C.c_int32), ("topk", C.c_int32), ("sm_scale", C.c_float),
+        ("q", C.c_void_p), ("stride_q_token", C.c_int64), ("kv", C.c_void_p),
+        ("indices", C.c_void_p), ("stride_indices_pair", C.c_int64),
+        ("attn_sink", C.c_void_p), ("topk_length", C.c_void_p),
+        ("w1", C.c_uint32 * 8), ("w2", C.c_uint32 * 8),
+        ("out", C.c_void_p), ("max_logits", C.c_void_p), ("lse", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+class SchedParams(C.Structure):
+    _fields_ = [
+        ("b", C.c_int32), ("s_q", C.c_int32), ("topk", C.c_int32), ("extra_topk", C.c_int32),
+        ("topk_length", C.c_void_p), ("extra_topk_length", C.c_void_p), ("num_sm_parts", C.c_int32),
+        ("sched_meta", C.c_void_p), ("num_splits", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+class DecodeParams(C.Structure):
+    _fields_ = [
+        ("b", C.c_int32), ("s_q", C.c_int32), ("topk", C.c_int32), ("extra_topk", C.c_int32),
+        ("sm_scale", C.c_float),
+        ("q", C.c_void_p), ("stride_q_b", C.c_int64), ("stride_q_s", C.c_int64),
+        ("kv", C.c_void_p), ("num_blocks", C.c_int32), ("page_block_size", C.c_int32),
+        ("stride_kv_block", C.c_int64),
+        ("indices", C.c_void_p), ("stride_indices_b", C.c_int64), ("stride_indices_s", C.c_int64),
+        ("topk_length", C.c_void_p), ("attn_sink", C.c_void_p),
+        ("extra_kv", C.c_void_p), ("extra_num_blocks", C.c_int32), ("extra_page_block_size", C.c_int32),
+        ("stride_extra_kv_block", C.c_int64),
+        ("extra_indices", C.c_void_p), ("stride_extra_indices_b", C.c_int64),
+        ("stride_extra_indices_s", C.c_int64), ("extra_topk_length", C.c_void_p),
+        ("w1", C.c_uint32 * 8), ("w2", C.c_uint32 * 8),
+        ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("sched_meta", C.c_void_p), ("num_splits", C.c_void_p), ("num_sm_parts", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m mxdsa_b200.build`")
+        L = C.CDLL(LIB_PATH)
+        L.mxdsa_status_string.restype = C.c_char_p
+        L.mxdsa_status_string.argtypes = [C.c_int]
+        L.mxdsa_last_cuda_error.restype = C.c_int
+        L.mxdsa_device_fault.argtypes = [C.c_void_p]
+        L.mxdsa_prefill_fwd.argtypes = [C.POINTER(PrefillParams)]
+        L.mxdsa_num_sm_parts.argtypes = [C.c_int, C.c_int]
+        L.mxdsa_decode_sched.argtypes = [C.POINTER(SchedParams)]
+        L.mxdsa_decode_workspace_bytes.restype = C.c_size_t
+        L.mxdsa_decode_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
+        L.mxdsa_decode_fwd.argtypes = [C.POINTER(DecodeParams)]
+        _lib = L
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        L = lib()
+        msg = L.mxdsa_status_string(status).decode()
+        raise RuntimeError(f"{what}: {msg} (status {status}, cuda error {L.mxdsa_last_cuda_error()})")
