@@ -11,14 +11,22 @@
 //   accumulators live in tensor memory: per CTA 128 lanes x (256 O + 2 x 64 P) columns; lane L
 //   holds row L%64, and column half L/64 (P: keys 64*(L/64).., O: dims 256*(L/64)..).
 //
-// Roles (warp-specialised, 8 warps per CTA)
-//   warp 0  gather producer : reads key indices, issues TMA gather4 row copies into the K/V ring
-//   warp 1  QK issuer (CTA 0, one thread); in CTA 1 idle
-//   warp 2  PV issuer (CTA 0, one thread); in CTA 1 idle
-//   warp 3  operand stager  : Q tile TMA + Q scale rows (per pair); K scale rows, key token
-//           scales and validity bits (per tile)
-//   warps 4-7 softmax       : P -> registers, running max with lazy rescale, exp2, token-scale,
-//           per-32-key UE8M0 requantisation to E4M3 S, O rescale, and the epilogue.
+// Roles (warp-specialised, 20 warps per CTA, 96 registers per thread)
+//   warps 0-3   K producers: read key indices and copy the selected rows of this CTA's 64 keys
+//               into a 3-deep K ring with 16-byte cp.async; one warp instruction moves one
+//               512-byte row straight into the 128-byte-swizzled operand layout.  Measured on a
+//               B200 this path sustains ~40 B/clk/SM of random 512-byte rows from L2, against
+//               ~21 B/clk/SM for TMA gather4 issued from the same SM.
+//   warps 4-7   V producers: same for the 256-byte halves of all 128 keys (2-deep V ring)
+//   warp 8      CTA 0: QK issuer for even tiles      CTA 1: relays "K rows landed" to CTA 0
+//   warp 9      CTA 0: QK issuer for odd tiles       (a tcgen05.mma costs one thread ~60 cycles
+//               of issue time, so two threads alternate tiles, each with its own P buffer)
+//   warp 10     CTA 0: PV issuer                     CTA 1: relays "V rows landed" to CTA 0
+//   warp 11     operand stager: Q tile TMA + Q scale rows (per pair); K scale rows, key token
+//               scales and validity bits (per tile)
+//   warps 12-19 softmax: P -> registers (each thread one 32-key block of one row), running max
+//               with lazy rescale, exp2, token-scale, per-32-key UE8M0 requantisation to E4M3 S,
+//               O rescale, and the epilogue.
 //
 // Numerical contract (identical to the reference kernels, reference file:line in brackets)
 //   * keys are consumed in numerical tiles of NT = 128 (prefill, topk >= 512) or 64 keys
@@ -50,17 +58,19 @@ static constexpr int kHeads = 64;
 static constexpr int kDim = 512;
 static constexpr int kRowBytes = 528;
 static constexpr int kTileKeys = 128;    // keys per tensor-core tile
-static constexpr int kStages = 2;        // K/V ring depth (64 KB per stage and CTA)
-static constexpr int kScStages = 4;      // scale/validity ring depth
-static constexpr int kThreads = 256;
+static constexpr int kKStages = 3;       // K ring depth (32 KB per stage and CTA)
+static constexpr int kVStages = 2;       // V ring depth (32 KB per stage and CTA)
+static constexpr int kScStages = 4;      // scale/validity ring depth; also the depth of the
+                                         // per-tile "QK done" / "PV done" barrier rings
+static constexpr int kThreads = 640;
 
 // tensor-memory columns
 static constexpr uint32_t kColO = 0;      // 256 columns
 static constexpr uint32_t kColP = 256;    // 2 buffers x 64
-static constexpr uint32_t kColQs = 384;   // 4: Q scale bytes 0-3 (rows 0-31, 32-63), bytes 4-7
-static constexpr uint32_t kColKs = 388;   // 4: K scale bytes 0-3 (keys 0-31, 32-63 of the half), 4-7
-static constexpr uint32_t kColSs = 392;   // 2 buffers x 4 (2 used)
-static constexpr uint32_t kColVs = 400;   // 8: w words 0-7
+static constexpr uint32_t kColQs = 384;   // 2 x 4 (one set per QK issuer): Q scale bytes 0-3 / 4-7 of rows 0-31, 32-63
+static constexpr uint32_t kColKs = 392;   // 2 x 4: K scale bytes 0-3 / 4-7 of keys 0-31, 32-63 of the half
+static constexpr uint32_t kColSs = 400;   // 2 buffers x 4 (2 used)
+static constexpr uint32_t kColVs = 408;   // 8: w words 0-7
 static constexpr uint32_t kTmemCols = 512;
 
 struct DeviceFault {
@@ -88,12 +98,12 @@ struct AttnParams {
     // prefill
     int s_kv;
     int num_pairs;
-    const uint8_t* kv_scales; // prefill: start of the 16-byte slot plane
+    const uint8_t* kv_scales; // prefill: start of the 16-byte slot plane (kv = data rows)
     // decode
     int b;
     int page_size, rows_per_block;            // rows_per_block = stride_block / 512
     int extra_topk, extra_page_size, extra_rows_per_block;
-    const uint8_t* kv;        // decode: pool base (scale slots live inside the pages)
+    const uint8_t* kv;        // prefill: data rows; decode: pool base (slots live inside the pages)
     const uint8_t* extra_kv;
     long long stride_block, extra_stride_block; // bytes
     const int* extra_indices;
@@ -103,12 +113,11 @@ struct AttnParams {
     const int* num_splits;    // [b+1]
     float* o_accum;           // [splits][s_q][64][512]
     float* lse_accum;         // [splits][s_q][64]
+    unsigned long long* prof; // profiling builds: [2 CTAs][64] stall cycles of cluster 0, else null
 };
 
 struct TensorMaps {
     CUtensorMap q;        // 5-D {128 B, 64 heads, 4 chunks, tokens, requests}
-    CUtensorMap kv;       // 2-D {512 B, rows}
-    CUtensorMap extra_kv; // decode only
 };
 
 // One unit of work for a CTA pair: a query pair and a range of 64-key blocks of its key list.
@@ -126,8 +135,8 @@ struct WorkItem {
 
 struct __align__(1024) SmemPlan {
     uint8_t q[4 * 64 * 128];                       // [chunk][head][128 B], 128-byte swizzle
-    uint8_t k[kStages][4 * 64 * 128];              // [chunk][key of this CTA][128 B]
-    uint8_t v[kStages][2 * 128 * 128];             // [chunk of this CTA][key][128 B]
+    uint8_t k[kKStages][4 * 64 * 128];             // [chunk][key of this CTA][128 B]
+    uint8_t v[kVStages][2 * 128 * 128];            // [chunk of this CTA][key][128 B]
     uint8_t s[2][64 * 128];                        // [row][128 keys], 128-byte swizzle
     __align__(128) uint32_t q_sf[64 * 4];          // scale rows for tcgen05.cp (64 rows x 16 B)
     __align__(128) uint32_t k_sf[kScStages][64 * 4];
@@ -135,24 +144,30 @@ struct __align__(1024) SmemPlan {
     __align__(128) uint32_t v_sf[2][64 * 4];
     __align__(16) float tok_scale[kScStages][kTileKeys];
     __align__(16) uint32_t valid[kScStages][4];
-    float xmax[2][128];                            // row-max exchange between the two key halves
-    float xl[128];                                 // l exchange at the end of a pair
+    float xmax[2][256];                            // per-row exchange between the four 32-key blocks
+    float xl[256];                                 // partial l exchange at the end of a pair
     uint64_t bar_q_landed;                         // local: Q bytes landed
     uint64_t bar_q_full;                           // CTA0: Q data + scale rows of both CTAs ready
-    uint64_t bar_q_empty;                          // both: last QK of the pair finished
-    uint64_t bar_k_full[kStages], bar_v_full[kStages];      // CTA0
-    uint64_t bar_k_empty[kStages], bar_v_empty[kStages];    // both
+    uint64_t bar_q_empty;                          // both: every QK of the pair finished (2 arrivals)
+    uint64_t bar_k_landed[kKStages];               // local: this CTA's K rows landed (128 arrivals)
+    uint64_t bar_v_landed[kVStages];               // local: this CTA's V rows landed
+    uint64_t bar_k_full[kKStages];                 // CTA0: CTA1's K rows landed
+    uint64_t bar_v_full[kVStages];                 // CTA0: CTA1's V rows landed
+    uint64_t bar_qk_done[kScStages];               // both: QK of tile g finished (ring by g % 4)
+    uint64_t bar_pv_done[kScStages];               // both: PV of tile g finished
+    uint64_t bar_pv_half[2];                       // both: first key half accumulated (64-key tiles)
     uint64_t bar_sc_full[kScStages];               // CTA0: K scale rows of both CTAs written
     uint64_t bar_tok_full[kScStages];              // local: token scales + validity written
-    uint64_t bar_sc_empty[kScStages];              // local: cp finished and softmax read the stage
-    uint64_t bar_p_full[2];                        // both
-    uint64_t bar_p_empty[2];                       // CTA0
+    uint64_t bar_tok_empty[kScStages];             // local: softmax has read the stage
+    uint64_t bar_p_empty[2];                       // CTA0: P buffer copied to registers
     uint64_t bar_s_full[2][2];                     // CTA0: [buffer][key half]
-    uint64_t bar_pv_half[2];                       // both: first key half of the tile accumulated
-    uint64_t bar_pv_done[2];                       // both: whole tile accumulated
     uint64_t bar_o_empty;                          // CTA0: epilogue has drained O
     uint32_t tmem_base;
     int abort_word;
+#ifdef MXDSA_PROFILE
+    unsigned long long prof[64];
+    long long ev[16][16];
+#endif
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -215,41 +230,80 @@ template <bool DECODE> struct WorkIter {
     }
 };
 
-// Index and validity of the key at position `j` (0..63) of 64-key block `blk` of a work item.
-// Returns the TMA row coordinate (-1 = no row, reads as zeros) and writes the byte address of
-// the key's 16-byte scale slot.
+// Key at position `j` (0..63) of 64-key block `blk` of a work item: is it attended, where are its
+// 512 data bytes (nullptr = no row, the operand rows are zero-filled) and its 16-byte scale slot.
 template <bool DECODE>
-__device__ __forceinline__ int key_lookup(const AttnParams& p, const WorkItem& w, int blk, int j, bool& valid,
-                                          const uint8_t*& slot) {
+__device__ __forceinline__ const uint8_t* key_lookup(const AttnParams& p, const WorkItem& w, int blk, int j,
+                                                     bool& valid, const uint8_t*& slot) {
     valid = false;
     slot = nullptr;
-    if (blk >= w.blk_end) return -1;
+    if (blk >= w.blk_end) return nullptr;
     if constexpr (!DECODE) {
         const int pos = blk * 64 + j;
-        if (pos >= p.topk) return -1;
+        if (pos >= p.topk) return nullptr;
         const int idx = __ldg(w.row + pos);
-        valid = idx >= 0 && idx < p.s_kv && pos < w.len;
-        if (idx >= 0 && idx < p.s_kv) slot = p.kv_scales + (long long)idx * 16;
-        return idx;  // out-of-range rows read as zeros; masked by `valid`
+        if (idx < 0 || idx >= p.s_kv) return nullptr;
+        valid = pos < w.len;
+        slot = p.kv_scales + (long long)idx * 16;
+        return p.kv + (long long)idx * kDim;
     } else {
         const bool extra = blk >= w.n_main_blocks;
         const int pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
         const int row_len = extra ? p.extra_topk : p.topk;
         const int idx = pos < row_len ? __ldg((extra ? w.erow : w.row) + pos) : -1;
         valid = idx != -1 && pos < (extra ? w.elen : w.len);
-        if (!valid) return -1;
+        if (!valid) return nullptr;
         const unsigned psz = extra ? p.extra_page_size : p.page_size;
         const unsigned page = (unsigned)idx / psz, in_page = (unsigned)idx % psz;
-        slot = (extra ? p.extra_kv : p.kv) + (long long)page * (extra ? p.extra_stride_block : p.stride_block) +
-               (long long)psz * kDim + (long long)in_page * 16;
-        return (int)(page * (unsigned)(extra ? p.extra_rows_per_block : p.rows_per_block) + in_page);
+        const uint8_t* pg = (extra ? p.extra_kv : p.kv) + (long long)page * (extra ? p.extra_stride_block : p.stride_block);
+        slot = pg + (long long)psz * kDim + (long long)in_page * 16;
+        return pg + (long long)in_page * kDim;
     }
 }
 
-// multiply this thread's 256 O columns (its tensor-memory lane) by f
+// packed fp32 pairs (one instruction for two lanes of data)
+__device__ __forceinline__ float2 f2_fma(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)),
+          "l"(reinterpret_cast<unsigned long long&>(c)));
+    return d;
+}
+__device__ __forceinline__ float2 f2_mul(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return d;
+}
+__device__ __forceinline__ float2 f2_add(float2 a, float2 b) {
+    float2 d;
+    asm("add.rn.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return d;
+}
+
+// 16-byte asynchronous copy global -> shared; `bytes` = 16 copies, 0 writes zeros.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// one arrival on `bar` once all cp.async issued so far by this thread have landed
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// multiply 128 O columns of this thread's tensor-memory lane, starting at lane_addr, by f
 __device__ __forceinline__ void rescale_o(uint32_t lane_addr, float f) {
 #pragma unroll 1
-    for (int c = 0; c < 256; c += 32) {
+    for (int c = 0; c < 128; c += 32) {
         uint32_t v[32];
         tmem_ld32(lane_addr + kColO + c, v);
         tmem_wait_ld();
@@ -260,12 +314,39 @@ __device__ __forceinline__ void rescale_o(uint32_t lane_addr, float f) {
     tmem_wait_st();
 }
 
+#ifdef MXDSA_PROFILE
+// per-wait stall accounting (cycles spent in each numbered wait, summed over the lanes' leader)
+#define MXDSA_PROF_BEGIN const long long prof_t0__ = clock64();
+#define MXDSA_PROF_END(code) \
+    if (lane == 0) atomicAdd(&sm.prof[(code)], (unsigned long long)(clock64() - prof_t0__));
+// event trace: cycle stamps of tiles 16..31 of this CTA (profiling builds only)
+#define MXDSA_EV(gtile, id) \
+    if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = clock64();
+#else
+#define MXDSA_PROF_BEGIN
+#define MXDSA_PROF_END(code)
+#define MXDSA_EV(gtile, id)
+#endif
+
+// latency-critical variant (issuers, softmax): polls instead of suspending
+#define MXDSA_WAIT_POLL(bar, parity, code)                                   \
+    do {                                                                     \
+        MXDSA_PROF_BEGIN                                                     \
+        if (!mbar_wait_poll(smem_u32(&(bar)), (parity), &sm.abort_word)) {   \
+            raise_fault(p, sm, (code));                                      \
+            goto done;                                                       \
+        }                                                                    \
+        MXDSA_PROF_END(code)                                                 \
+    } while (0)
+
 #define MXDSA_WAIT(bar, parity, code)                                   \
     do {                                                                \
+        MXDSA_PROF_BEGIN                                                \
         if (!mbar_wait(smem_u32(&(bar)), (parity), &sm.abort_word)) {   \
             raise_fault(p, sm, (code));                                 \
             goto done;                                                  \
         }                                                               \
+        MXDSA_PROF_END(code)                                            \
     } while (0)
 
 __device__ __noinline__ void raise_fault(const AttnParams& p, SmemPlan& sm, int code) {
@@ -284,37 +365,44 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
     const uint32_t cta = cluster_cta_rank();
-    const uint32_t peer = cta ^ 1u;
 
     // ------------------------------------------------------------------ set-up
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&sm.bar_q_landed), 1);
         mbar_init(smem_u32(&sm.bar_q_full), 2);
-        mbar_init(smem_u32(&sm.bar_q_empty), 1);
-        for (int i = 0; i < kStages; ++i) {
-            mbar_init(smem_u32(&sm.bar_k_full[i]), 2);
-            mbar_init(smem_u32(&sm.bar_v_full[i]), 2);
-            mbar_init(smem_u32(&sm.bar_k_empty[i]), 1);
-            mbar_init(smem_u32(&sm.bar_v_empty[i]), 1);
+        mbar_init(smem_u32(&sm.bar_q_empty), 2);
+        for (int i = 0; i < kKStages; ++i) {
+            mbar_init(smem_u32(&sm.bar_k_landed[i]), 128);
+            mbar_init(smem_u32(&sm.bar_k_full[i]), 1);
+        }
+        for (int i = 0; i < kVStages; ++i) {
+            mbar_init(smem_u32(&sm.bar_v_landed[i]), 128);
+            mbar_init(smem_u32(&sm.bar_v_full[i]), 1);
         }
         for (int i = 0; i < kScStages; ++i) {
+            mbar_init(smem_u32(&sm.bar_qk_done[i]), 1);
+            mbar_init(smem_u32(&sm.bar_pv_done[i]), 1);
             mbar_init(smem_u32(&sm.bar_sc_full[i]), 2);
             mbar_init(smem_u32(&sm.bar_tok_full[i]), 1);
-            mbar_init(smem_u32(&sm.bar_sc_empty[i]), 1 + 4);
+            mbar_init(smem_u32(&sm.bar_tok_empty[i]), 8);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&sm.bar_p_full[i]), 1);
-            mbar_init(smem_u32(&sm.bar_p_empty[i]), 8);
-            mbar_init(smem_u32(&sm.bar_s_full[i][0]), 8);
-            mbar_init(smem_u32(&sm.bar_s_full[i][1]), 8);
+            mbar_init(smem_u32(&sm.bar_p_empty[i]), 16);
+            mbar_init(smem_u32(&sm.bar_s_full[i][0]), 16);
+            mbar_init(smem_u32(&sm.bar_s_full[i][1]), 16);
             mbar_init(smem_u32(&sm.bar_pv_half[i]), 1);
-            mbar_init(smem_u32(&sm.bar_pv_done[i]), 1);
         }
-        mbar_init(smem_u32(&sm.bar_o_empty), 8);
+        mbar_init(smem_u32(&sm.bar_o_empty), 16);
         sm.abort_word = 0;
+#ifdef MXDSA_PROFILE
+        for (int i = 0; i < 64; ++i) sm.prof[i] = 0;
+#endif
         fence_mbar_init();
     }
-    if (warp == 3) {
+#ifdef MXDSA_PROFILE
+    const long long prof_kernel_t0 = clock64();
+#endif
+    if (warp == 11) {
         // V dimension scales: rows 0-31 feed lane quadrants 0,1 (dims of CTA 0 = w1), rows 32-63
         // quadrants 2,3 (dims of CTA 1 = w2); every row of a group is the same four words.
         for (int i = lane; i < 64; i += 32) {
@@ -325,15 +413,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             }
         }
         fence_proxy_async_smem();
-    }
-    if (warp == 0 && lane == 0) {
-        prefetch_tensormap(&maps.q);
-        prefetch_tensormap(&maps.kv);
-        if (DECODE) prefetch_tensormap(&maps.extra_kv);
+        if (lane == 0) prefetch_tensormap(&maps.q);
     }
     __syncthreads();
     cluster_sync();
-    if (warp == 2) {
+    if (warp == 10) {
         tmem_alloc<2>(smem_u32(&sm.tmem_base), kTmemCols);
         tmem_relinquish<2>();
     }
@@ -348,168 +432,233 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     const uint64_t desc_sf = smem_desc_base(0, 128, 0);       // scale rows, 16 bytes each
 
     // ------------------------------------------------------------------ roles
-    if (warp == 0) {
-        // ===================== gather producer =====================
+    if (warp < 4) {
+        // ===================== K producers (warps 0-3) =====================
+        // keys 64*cta + 16*warp + i (i < 16) of the tile, whole 512-byte rows, one per instruction;
+        // lane L writes byte chunk L of the row -> chunk tile L/8, 16-byte column (L%8) ^ (row%8).
         WorkIter<DECODE> it(p);
         WorkItem w;
-        uint32_t gt = 0;  // tiles issued so far (ring position)
-        const uint32_t k_full0 = map_to_cta(smem_u32(&sm.bar_k_full[0]), 0);
-        const uint32_t v_full0 = map_to_cta(smem_u32(&sm.bar_v_full[0]), 0);
+        uint32_t gt = 0;  // tiles issued so far
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+            const int key = 64 * (int)cta + 16 * warp + (lane & 15);
+            bool valid;
+            const uint8_t* slot;
+            const uint8_t* ptr = key_lookup<DECODE>(p, w, w.blk_begin + key / 64, key % 64, valid, slot);
             for (int t = 0; t < ntiles; ++t, ++gt) {
-                const uint32_t s = gt % kStages, ph = (gt / kStages) & 1;
-                // lane L owns keys 4L..4L+3 of the tile (block = L/16)
-                int coord[4];
-                const int blk = w.blk_begin + 2 * t + lane / 16;
-                bool extra_pool = false;
-                if constexpr (DECODE) extra_pool = blk >= w.n_main_blocks;
+                const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
+                const uint8_t* ptr_next = nullptr;
+                if (t + 1 < ntiles)   // prefetch the next tile's row addresses
+                    ptr_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + key / 64, key % 64, valid, slot);
+                if (gt >= kKStages) {   // stage s was last used by tile gt-3
+                    const uint32_t g = gt - kKStages;
+                    MXDSA_WAIT(sm.bar_qk_done[g % kScStages], (g / kScStages) & 1, 10);
+                }
+                if (warp == 0 && lane == 0) { MXDSA_EV(gt, 0) }
+                const uint32_t kbase = smem_u32(sm.k[s]) + (lane / 8) * 8192;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    bool valid;
-                    const uint8_t* slot;
-                    coord[i] = key_lookup<DECODE>(p, w, blk, (lane % 16) * 4 + i, valid, slot);
+                for (int i = 0; i < 16; ++i) {
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), i));
+                    const int r = 16 * warp + i;
+                    cp_async16(kbase + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + lane * 16 : p.kv,
+                               src ? 16u : 0u);
                 }
-                // K: keys of this CTA's half (block `cta`), 16 groups x 4 chunks = 2 copies per lane
-                const int src_lane = cta * 16 + lane % 16;
-                int kc[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) kc[i] = __shfl_sync(0xffffffffu, coord[i], src_lane);
-                const bool k_extra = __shfl_sync(0xffffffffu, (int)extra_pool, src_lane) != 0;
-                MXDSA_WAIT(sm.bar_k_empty[s], ph ^ 1, 10);
-                if (lane == 0) {
-                    const uint32_t bar = k_full0 + s * 8;
-                    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar),
-                                 "r"(4 * 64 * 128)
-                                 : "memory");
-                }
-                {
-                    const void* map = (DECODE && k_extra) ? &maps.extra_kv : &maps.kv;
-                    const int g = lane % 16;
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int chunk = 2 * (lane / 16) + j;
-                        tma_gather4_pair(smem_u32(&sm.k[s][chunk * 8192 + g * 512]), map, chunk * 128, kc[0], kc[1],
-                                         kc[2], kc[3], k_full0 + s * 8, kEvictLast);
-                    }
-                }
-                // V: all 128 keys, this CTA's two 128-byte chunks
-                MXDSA_WAIT(sm.bar_v_empty[s], ph ^ 1, 11);
-                if (lane == 0) {
-                    const uint32_t bar = v_full0 + s * 8;
-                    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar),
-                                 "r"(2 * 128 * 128)
-                                 : "memory");
-                }
-                {
-                    const void* map = (DECODE && extra_pool) ? &maps.extra_kv : &maps.kv;
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-                        tma_gather4_pair(smem_u32(&sm.v[s][j * 16384 + lane * 512]), map, (2 * cta + j) * 128,
-                                         coord[0], coord[1], coord[2], coord[3], v_full0 + s * 8, kEvictLast);
-                }
+                cp_async_arrive(smem_u32(&sm.bar_k_landed[s]));
+                if (warp == 0 && lane == 0) { MXDSA_EV(gt, 1) }
+                ptr = ptr_next;
             }
         }
-    } else if (warp == 1) {
-        // ===================== QK issuer (CTA 0) =====================
+    } else if (warp < 8) {
+        // ===================== V producers (warps 4-7) =====================
+        // keys 32*pw + 2i, 2i+1 (i < 16), bytes 256*cta .. +255, two keys per instruction;
+        // lane L writes chunk tile (L%16)/8 of key 2i + L/16.
+        const int pw = warp - 4;
+        WorkIter<DECODE> it(p);
+        WorkItem w;
+        uint32_t gt = 0;
+        while (it.template next<NT>(w)) {
+            const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
+            if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+            const int key = 32 * pw + lane;
+            bool valid;
+            const uint8_t* slot;
+            const uint8_t* ptr = key_lookup<DECODE>(p, w, w.blk_begin + key / 64, key % 64, valid, slot);
+            for (int t = 0; t < ntiles; ++t, ++gt) {
+                const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
+                const uint8_t* ptr_next = nullptr;
+                if (t + 1 < ntiles)
+                    ptr_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + key / 64, key % 64, valid, slot);
+                if (gt >= kVStages) {   // stage s was last used by tile gt-2
+                    const uint32_t g = gt - kVStages;
+                    MXDSA_WAIT(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 11);
+                }
+                if (pw == 0 && lane == 0) { MXDSA_EV(gt, 2) }
+                const uint32_t vbase = smem_u32(sm.v[s]) + ((lane & 15) / 8) * 16384;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), 2 * i + lane / 16));
+                    const int r = 32 * pw + 2 * i + lane / 16;
+                    cp_async16(vbase + r * 128 + (((lane & 7) ^ (r & 7)) << 4),
+                               src ? src + 256 * cta + (lane & 15) * 16 : p.kv, src ? 16u : 0u);
+                }
+                cp_async_arrive(smem_u32(&sm.bar_v_landed[s]));
+                if (pw == 0 && lane == 0) { MXDSA_EV(gt, 3) }
+                ptr = ptr_next;
+                (void)ph;
+            }
+        }
+    } else if (warp == 8 || warp == 9) {
         if (cta == 0 && lane == 0) {
+            // ===================== QK issuers (CTA 0): warp 8 even tiles, warp 9 odd tiles ==========
+            const uint32_t e = warp - 8;   // tile parity = P buffer = scale column set owned by this issuer
             WorkIter<DECODE> it(p);
             WorkItem w;
             uint32_t gt = 0, gw = 0;
-            const uint32_t p_full_peer = map_to_cta(smem_u32(&sm.bar_p_full[0]), 1);
-            const uint32_t k_empty_peer = map_to_cta(smem_u32(&sm.bar_k_empty[0]), 1);
-            const uint32_t sc_empty_peer = map_to_cta(smem_u32(&sm.bar_sc_empty[0]), 1);
+            const uint32_t qk_done_peer = map_to_cta(smem_u32(&sm.bar_qk_done[0]), 1);
             const uint32_t q_empty_peer = map_to_cta(smem_u32(&sm.bar_q_empty), 1);
             const uint64_t a_base = smem_desc(desc_k128, smem_u32(sm.q));
             while (it.template next<NT>(w)) {
                 const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
-            if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-                MXDSA_WAIT(sm.bar_q_full, gw & 1, 20);
-                tc_fence_after();
-                tmem_cp_sf_pair(tmem + kColQs, smem_desc(desc_sf, smem_u32(sm.q_sf)));
+                if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+                // Both issuers observe every phase of q_full, also for a pair in which they own no
+                // tile: a parity wait that skipped a phase would be satisfied by the stale one.
+                MXDSA_WAIT_POLL(sm.bar_q_full, gw & 1, 20);
+                bool mine = false;
                 for (int t = 0; t < ntiles; ++t, ++gt) {
-                    const uint32_t s = gt % kStages, ph = (gt / kStages) & 1;
+                    if ((gt & 1) != e) continue;
+                    const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
                     const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
-                    const uint32_t b = gt & 1, bph = (gt >> 1) & 1;
-                    MXDSA_WAIT(sm.bar_sc_full[sc], sph, 21);
-                    MXDSA_WAIT(sm.bar_p_empty[b], bph ^ 1, 22);
-                    MXDSA_WAIT(sm.bar_k_full[s], ph, 23);
+                    const uint32_t bph = (gt >> 1) & 1;
+                    if (!mine) {   // first own tile of this pair: the pair's Q scale rows
+                        tc_fence_after();
+                        tmem_cp_sf_pair(tmem + kColQs + 4 * e, smem_desc(desc_sf, smem_u32(sm.q_sf)));
+                        mine = true;
+                    }
+                    MXDSA_WAIT_POLL(sm.bar_sc_full[sc], sph, 21);
+                    MXDSA_WAIT_POLL(sm.bar_p_empty[e], bph ^ 1, 22);
+                    MXDSA_WAIT_POLL(sm.bar_k_landed[s], ph, 23);
+                    MXDSA_WAIT_POLL(sm.bar_k_full[s], ph, 24);
+                    fence_proxy_async_smem();   // rows written by cp.async are read by the tensor core
+                    MXDSA_EV(gt, 6)
                     tc_fence_after();
-                    tmem_cp_sf_pair(tmem + kColKs, smem_desc(desc_sf, smem_u32(sm.k_sf[sc])));
+                    tmem_cp_sf_pair(tmem + kColKs + 4 * e, smem_desc(desc_sf, smem_u32(sm.k_sf[sc])));
                     const uint64_t b_base = smem_desc(desc_k128, smem_u32(sm.k[s]));
 #pragma unroll
                     for (int kk = 0; kk < 16; ++kk) {
                         // Q bytes (kk%8)*64 + (kk/8)*32 of the row meet K bytes 32*kk
                         const uint32_t a_off = ((kk % 8) / 2) * 8192 + ((kk % 8) % 2) * 64 + (kk / 8) * 32;
                         const uint32_t b_off = (kk / 4) * 8192 + (kk % 4) * 32;
-                        mma_mxf8<2>(tmem + kColP + b * 64, a_base + (a_off >> 4), b_base + (b_off >> 4),
-                                    mx_idesc(128, 128, false, kk & 3, (kk / 2) & 3), tmem + kColQs + 2 * ((kk / 4) & 1),
-                                    tmem + kColKs + 2 * (kk / 8), kk != 0);
+                        mma_mxf8<2>(tmem + kColP + e * 64, a_base + (a_off >> 4), b_base + (b_off >> 4),
+                                    mx_idesc(128, 128, false, kk & 3, (kk / 2) & 3),
+                                    tmem + kColQs + 4 * e + 2 * ((kk / 4) & 1), tmem + kColKs + 4 * e + 2 * (kk / 8),
+                                    kk != 0);
                     }
-                    mma_commit<2>(smem_u32(&sm.bar_p_full[b]));
-                    mma_commit<2>(p_full_peer + b * 8);
-                    mma_commit<2>(smem_u32(&sm.bar_k_empty[s]));
-                    mma_commit<2>(k_empty_peer + s * 8);
-                    mma_commit<2>(smem_u32(&sm.bar_sc_empty[sc]));
-                    mma_commit<2>(sc_empty_peer + sc * 8);
+                    mma_commit<2>(smem_u32(&sm.bar_qk_done[sc]));
+                    mma_commit<2>(qk_done_peer + sc * 8);
+                    MXDSA_EV(gt, 7)
                 }
-                mma_commit<2>(smem_u32(&sm.bar_q_empty));
-                mma_commit<2>(q_empty_peer);
+                // Q may be overwritten once both issuers' QKs of this pair have finished
+                if (mine) {
+                    mma_commit<2>(smem_u32(&sm.bar_q_empty));
+                    mma_commit<2>(q_empty_peer);
+                } else {
+                    mbar_arrive(smem_u32(&sm.bar_q_empty));
+                    mbar_arrive_cluster(q_empty_peer);
+                }
                 ++gw;
             }
+        } else if (cta == 1 && warp == 8 && lane == 0) {
+            // ===================== K relay (CTA 1) =====================
+            WorkIter<DECODE> it(p);
+            WorkItem w;
+            uint32_t gt = 0;
+            const uint32_t k_full0 = map_to_cta(smem_u32(&sm.bar_k_full[0]), 0);
+            while (it.template next<NT>(w)) {
+                const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
+                if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+                for (int t = 0; t < ntiles; ++t, ++gt) {
+                    const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
+                    MXDSA_WAIT(sm.bar_k_landed[s], ph, 12);
+                    fence_proxy_async_smem();
+                    mbar_arrive_cluster(k_full0 + s * 8);
+                }
+            }
         }
-    } else if (warp == 2) {
-        // ===================== PV issuer (CTA 0) =====================
+    } else if (warp == 10) {
         if (cta == 0 && lane == 0) {
+            // ===================== PV issuer (CTA 0) =====================
             WorkIter<DECODE> it(p);
             WorkItem w;
             uint32_t gt = 0, gw = 0;
             const uint32_t pv_half_peer = map_to_cta(smem_u32(&sm.bar_pv_half[0]), 1);
             const uint32_t pv_done_peer = map_to_cta(smem_u32(&sm.bar_pv_done[0]), 1);
-            const uint32_t v_empty_peer = map_to_cta(smem_u32(&sm.bar_v_empty[0]), 1);
             tmem_cp_sf_pair(tmem + kColVs, smem_desc(desc_sf, smem_u32(sm.v_sf[0])));
             tmem_cp_sf_pair(tmem + kColVs + 4, smem_desc(desc_sf, smem_u32(sm.v_sf[1])));
             while (it.template next<NT>(w)) {
                 const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
-            if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-                MXDSA_WAIT(sm.bar_o_empty, (gw & 1) ^ 1, 30);
+                if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+                MXDSA_WAIT_POLL(sm.bar_o_empty, (gw & 1) ^ 1, 30);
                 tc_fence_after();
                 for (int t = 0; t < ntiles; ++t, ++gt) {
-                    const uint32_t s = gt % kStages, ph = (gt / kStages) & 1;
+                    const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
                     const uint32_t b = gt & 1, bph = (gt >> 1) & 1;
-                    MXDSA_WAIT(sm.bar_v_full[s], ph, 31);
+                    const uint32_t sc = gt % kScStages;
+                    MXDSA_WAIT_POLL(sm.bar_v_landed[s], ph, 31);
+                    MXDSA_WAIT_POLL(sm.bar_v_full[s], ph, 34);
+                    fence_proxy_async_smem();
                     const uint64_t a_base = smem_desc(desc_k128, smem_u32(sm.s[b]));
                     const uint64_t b_base = smem_desc(desc_v, smem_u32(sm.v[s]));
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        MXDSA_WAIT(sm.bar_s_full[b][h], bph, 32 + h);
-                        tc_fence_after();
-                        tmem_cp_sf_pair(tmem + kColSs + 4 * b, smem_desc(desc_sf, smem_u32(sm.s_sf[b])));
+                        if (NT == 64 || h == 1) {   // 128-key tiles: one wait, after both halves are in
+                            MXDSA_WAIT_POLL(sm.bar_s_full[b][h], bph, 32 + h);
+                            MXDSA_EV(gt, 13 + h)
+                            tc_fence_after();
+                            tmem_cp_sf_pair(tmem + kColSs + 4 * b, smem_desc(desc_sf, smem_u32(sm.s_sf[b])));
+                        }
+                        if (NT == 128 && h == 0) continue;
 #pragma unroll
-                        for (int ks = 2 * h; ks < 2 * h + 2; ++ks) {
+                        for (int ks = (NT == 64 ? 2 * h : 0); ks < 2 * h + 2; ++ks) {
 #pragma unroll
                             for (int n = 0; n < 2; ++n) {
                                 mma_mxf8<2>(tmem + kColO + n * 128, a_base + ((ks * 32) >> 4),
                                             b_base + ((n * 16384 + ks * 4096) >> 4),
-                                            mx_idesc(128, 256, true, ks, NT == 64 ? (ks & 1) : ks), tmem + kColSs + 4 * b,
-                                            tmem + kColVs + 4 * n, !(t == 0 && ks == 0));
+                                            mx_idesc(128, 256, true, ks, NT == 64 ? (ks & 1) : ks),
+                                            tmem + kColSs + 4 * b, tmem + kColVs + 4 * n, !(t == 0 && ks == 0));
                             }
                         }
-                        if (h == 0) {
+                        if (NT == 64 && h == 0) {
                             mma_commit<2>(smem_u32(&sm.bar_pv_half[b]));
                             mma_commit<2>(pv_half_peer + b * 8);
                         }
                     }
-                    mma_commit<2>(smem_u32(&sm.bar_pv_done[b]));
-                    mma_commit<2>(pv_done_peer + b * 8);
-                    mma_commit<2>(smem_u32(&sm.bar_v_empty[s]));
-                    mma_commit<2>(v_empty_peer + s * 8);
+                    mma_commit<2>(smem_u32(&sm.bar_pv_done[sc]));
+                    mma_commit<2>(pv_done_peer + sc * 8);
+                    MXDSA_EV(gt, 15)
                 }
                 ++gw;
             }
+        } else if (cta == 1 && lane == 0) {
+            // ===================== V relay (CTA 1) =====================
+            WorkIter<DECODE> it(p);
+            WorkItem w;
+            uint32_t gt = 0;
+            const uint32_t v_full0 = map_to_cta(smem_u32(&sm.bar_v_full[0]), 0);
+            while (it.template next<NT>(w)) {
+                const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
+                if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+                for (int t = 0; t < ntiles; ++t, ++gt) {
+                    const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
+                    MXDSA_WAIT(sm.bar_v_landed[s], ph, 13);
+                    fence_proxy_async_smem();
+                    mbar_arrive_cluster(v_full0 + s * 8);
+                }
+            }
         }
-    } else if (warp == 3) {
+    } else if (warp == 11) {
         // ===================== operand stager =====================
         WorkIter<DECODE> it(p);
         WorkItem w;
@@ -559,7 +708,10 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     sv[j] = slot != nullptr ? __ldg(reinterpret_cast<const uint2*>(slot)) : make_uint2(0u, 0u);
                     vbits[j] = __ballot_sync(0xffffffffu, valid);
                 }
-                MXDSA_WAIT(sm.bar_sc_empty[sc], sph ^ 1, 42);
+                if (gt >= kScStages) {   // the stage was last used by tile gt-4: its cp and its readers are done
+                    MXDSA_WAIT(sm.bar_qk_done[sc], sph ^ 1, 42);
+                    MXDSA_WAIT(sm.bar_tok_empty[sc], sph ^ 1, 43);
+                }
                 // rows for tcgen05.cp: row r = (half of the tile)*32 + L holds keys (half*64 + L) and (+32):
                 // {bytes0-3[k0], bytes0-3[k1], bytes4-7[k0], bytes4-7[k1]}
                 *reinterpret_cast<uint4*>(&sm.k_sf[sc][lane * 4]) = make_uint4(sv[0].x, sv[1].x, sv[0].y, sv[1].y);
@@ -578,15 +730,21 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             ++gw;
         }
     } else {
-        // ===================== softmax + epilogue (warps 4-7) =====================
-        const int q4 = warp - 4;                 // lane quadrant of tensor memory
+        // ===================== softmax + epilogue (warps 12-19) =====================
+        // Two warps share each tensor-memory lane quadrant: warp w works on lanes 32*(w%4).. and on
+        // 32-column group cg = (w-12)/4 of the lane's 64 P columns, i.e. on ONE 32-key block of the
+        // tile (block kb = 2*half + cg), which is also one UE8M0 scale group of S.
+        const int q4 = warp & 3;                 // lane quadrant of tensor memory
+        const int cg = (warp - 12) >> 2;         // column group inside the lane
         const int L = q4 * 32 + lane;            // tensor-memory lane
         const int row = L % 64;                  // head
         const int half = L / 64;                 // key half of a tile / dim half of O
+        const int kb = 2 * half + cg;            // 32-key block of the tile handled by this thread
         const uint32_t lane_addr = tmem + (uint32_t(q4 * 32) << 16);
         const uint32_t p_empty0 = map_to_cta(smem_u32(&sm.bar_p_empty[0]), 0);
         const uint32_t s_full0 = map_to_cta(smem_u32(&sm.bar_s_full[0][0]), 0);
         const uint32_t o_empty0 = map_to_cta(smem_u32(&sm.bar_o_empty), 0);
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         WorkIter<DECODE> it(p);
         WorkItem w;
         uint32_t gt = 0;
@@ -597,33 +755,42 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             for (int t = 0; t < ntiles; ++t, ++gt) {
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                 const uint32_t b = gt & 1, bph = (gt >> 1) & 1;
-                MXDSA_WAIT(sm.bar_tok_full[sc], sph, 50);
-                const uint32_t v0 = sm.valid[sc][2 * half], v1 = sm.valid[sc][2 * half + 1];
-                MXDSA_WAIT(sm.bar_p_full[b], bph, 51);
+                MXDSA_WAIT_POLL(sm.bar_tok_full[sc], sph, 50);
+                const uint32_t vmask = sm.valid[sc][kb];
+                MXDSA_WAIT_POLL(sm.bar_qk_done[sc], sph, 51);
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 8) }
                 tc_fence_after();
-                float x[64];
-                tmem_ld32(lane_addr + kColP + b * 64, reinterpret_cast<uint32_t*>(x));
-                tmem_ld32(lane_addr + kColP + b * 64 + 32, reinterpret_cast<uint32_t*>(x + 32));
+                float x[32];
+                tmem_ld32(lane_addr + kColP + b * 64 + cg * 32, reinterpret_cast<uint32_t*>(x));
                 tmem_wait_ld();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(p_empty0 + b * 8);
-                float own_max = -CUDART_INF_F;
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 9) }
+                if (vmask != 0xffffffffu) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const bool ok = ((i < 32 ? v0 : v1) >> (i & 31)) & 1u;
-                    x[i] = ok ? x[i] : -CUDART_INF_F;
-                    own_max = fmaxf(own_max, x[i]);
+                    for (int i = 0; i < 32; ++i) x[i] = ((vmask >> i) & 1u) ? x[i] : -CUDART_INF_F;
                 }
-                own_max *= p.scale_log2;
-                sm.xmax[gt & 1][L] = own_max;
-                named_bar_sync(1, 128);
-                const float peer_max = sm.xmax[gt & 1][L ^ 64];
+                float mx4[4] = {x[0], x[1], x[2], x[3]};
+#pragma unroll
+                for (int i = 4; i < 32; i += 4) {
+                    mx4[0] = fmaxf(mx4[0], x[i]);
+                    mx4[1] = fmaxf(mx4[1], x[i + 1]);
+                    mx4[2] = fmaxf(mx4[2], x[i + 2]);
+                    mx4[3] = fmaxf(mx4[3], x[i + 3]);
+                }
+                const float own_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+                float* xm = sm.xmax[gt & 1];
+                xm[kb * 64 + row] = own_max;
+                named_bar_sync(1, 256);
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 10) }
+                const float t0 = fmaxf(xm[row], xm[64 + row]);          // key half 0 (blocks 0, 1)
+                const float t1 = fmaxf(xm[128 + row], xm[192 + row]);   // key half 1 (blocks 2, 3)
                 // numerical tiles: NT = 128 -> one per tensor-core tile; NT = 64 -> key half 0 then 1
                 float m_used, scale0 = 1.f, scale1 = 1.f;
                 bool grow0, grow1 = false;
                 if constexpr (NT == 128) {
-                    const float tmax = fmaxf(own_max, peer_max);
+                    const float tmax = fmaxf(t0, t1);
                     real_m = fmaxf(real_m, tmax);
                     grow0 = __any_sync(0xffffffffu, tmax - m > 6.0f);
                     const float nm = grow0 ? fmaxf(m, tmax) : m;
@@ -631,8 +798,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     m = nm;
                     m_used = m;
                 } else {
-                    const float t0 = half == 0 ? own_max : peer_max;
-                    const float t1 = half == 0 ? peer_max : own_max;
                     real_m = fmaxf(real_m, fmaxf(t0, t1));
                     grow0 = __any_sync(0xffffffffu, t0 - m > 6.0f);
                     const float m1 = grow0 ? fmaxf(m, t0) : m;
@@ -643,38 +808,43 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     m_used = half == 0 ? m1 : m2;
                     m = m2;
                 }
-                // probabilities, key-scaled, re-quantised per 32 keys
-                const float* tok = &sm.tok_scale[sc][half * 64];
-                float sum = 0.f;
-                uint32_t s8[16];
-                uint32_t e_bytes = 0;
+                // probabilities, key-scaled, re-quantised (this thread = one 32-key scale group)
+                const float2 negm2 = make_float2(-m_used, -m_used);
+                const float4* tok4 = reinterpret_cast<const float4*>(&sm.tok_scale[sc][kb * 32]);
+                float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+                float am4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    float amax = 0.f;
-                    float partial[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int c = g * 32 + i;
-                        const float pv = ex2_approx(fmaf(x[c], p.scale_log2, -m_used));
-                        partial[i & 3] += pv;
-                        const float sv = pv * tok[c];
-                        amax = fmaxf(amax, sv);
-                        x[c] = sv;
-                    }
-                    sum += (partial[0] + partial[1]) + (partial[2] + partial[3]);
-                    uint32_t e = cvt_ue8m0_roundup(amax > 0.f ? __fdividef(amax, 448.0f) : 1.0f);
-                    e = max(e, 61u);
-                    e_bytes |= e << (8 * g);
-                    const float mul = __uint_as_float((254u - e) << 23);
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const int c = g * 32 + i;
-                        const uint32_t lo = cvt_e4m3x2(x[c] * mul, x[c + 1] * mul);
-                        const uint32_t hi = cvt_e4m3x2(x[c + 2] * mul, x[c + 3] * mul);
-                        s8[c / 4] = lo | (hi << 16);
-                    }
+                for (int i = 0; i < 32; i += 4) {
+                    const float4 tk = tok4[i / 4];
+                    float2 a = f2_fma(make_float2(x[i], x[i + 1]), scale2, negm2);
+                    float2 c = f2_fma(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
+                    a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
+                    c = make_float2(ex2_approx(c.x), ex2_approx(c.y));
+                    sum2[0] = f2_add(sum2[0], a);
+                    sum2[1] = f2_add(sum2[1], c);
+                    a = f2_mul(a, make_float2(tk.x, tk.y));
+                    c = f2_mul(c, make_float2(tk.z, tk.w));
+                    am4[0] = fmaxf(am4[0], a.x);
+                    am4[1] = fmaxf(am4[1], a.y);
+                    am4[2] = fmaxf(am4[2], c.x);
+                    am4[3] = fmaxf(am4[3], c.y);
+                    x[i] = a.x; x[i + 1] = a.y; x[i + 2] = c.x; x[i + 3] = c.y;
                 }
-                // l bookkeeping: every m update rescales both halves' partial sums
+                const float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
+                const float2 s2 = f2_add(sum2[0], sum2[1]);
+                const float sum = s2.x + s2.y;
+                uint32_t e = cvt_ue8m0_roundup(amax > 0.f ? __fdividef(amax, 448.0f) : 1.0f);
+                e = max(e, 61u);
+                const float mulf = __uint_as_float((254u - e) << 23);
+                const float2 mul2 = make_float2(mulf, mulf);
+                uint32_t s8[8];
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    const float2 a = f2_mul(make_float2(x[i], x[i + 1]), mul2);
+                    const float2 c = f2_mul(make_float2(x[i + 2], x[i + 3]), mul2);
+                    s8[i / 4] = (uint32_t)cvt_e4m3x2(a.x, a.y) | ((uint32_t)cvt_e4m3x2(c.x, c.y) << 16);
+                }
+                // l bookkeeping: every m update rescales all partial sums of the row
                 if constexpr (NT == 128) {
                     l = fmaf(l, scale0, sum);
                 } else {
@@ -682,53 +852,54 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     else l = fmaf(l * scale0, scale1, sum);
                 }
                 // S buffer b is free once the PV of tile gt-2 has finished
-                if (gt >= 2) MXDSA_WAIT(sm.bar_pv_done[b], bph ^ 1, 52);
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 11) }
+                if (gt >= 2) {
+                    const uint32_t g = gt - 2;
+                    MXDSA_WAIT_POLL(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 52);
+                }
                 {
                     uint8_t* srow = sm.s[b];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + i * 16)) =
-                            make_uint4(s8[4 * i], s8[4 * i + 1], s8[4 * i + 2], s8[4 * i + 3]);
-                    // scale rows: row (row%32) and its copy at +32; word row/32; bytes 2*half, 2*half+1
-                    uint16_t* w0 = reinterpret_cast<uint16_t*>(&sm.s_sf[b][(row % 32) * 4 + row / 32]) + half;
-                    uint16_t* w1 = reinterpret_cast<uint16_t*>(&sm.s_sf[b][(32 + row % 32) * 4 + row / 32]) + half;
-                    *w0 = (uint16_t)e_bytes;
-                    *w1 = (uint16_t)e_bytes;
+                    *reinterpret_cast<uint4*>(srow + swz128(row, kb * 32)) = make_uint4(s8[0], s8[1], s8[2], s8[3]);
+                    *reinterpret_cast<uint4*>(srow + swz128(row, kb * 32 + 16)) = make_uint4(s8[4], s8[5], s8[6], s8[7]);
+                    // scale rows: row (row%32) and its copy at +32; word row/32; byte kb
+                    reinterpret_cast<uint8_t*>(&sm.s_sf[b][(row % 32) * 4 + row / 32])[kb] = (uint8_t)e;
+                    reinterpret_cast<uint8_t*>(&sm.s_sf[b][(32 + row % 32) * 4 + row / 32])[kb] = (uint8_t)e;
                 }
-                // O rescale before the first key half is accumulated
+                // O rescale before the first key half is accumulated (this thread: 128 of the lane's columns)
                 if (grow0 && t > 0) {
-                    MXDSA_WAIT(sm.bar_pv_done[b ^ 1], ((gt - 1) >> 1) & 1, 53);
+                    MXDSA_WAIT_POLL(sm.bar_pv_done[(gt - 1) % kScStages], ((gt - 1) / kScStages) & 1, 53);
                     tc_fence_after();
-                    rescale_o(lane_addr, scale0);
+                    rescale_o(lane_addr + cg * 128, scale0);
                     tc_fence_before();
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(s_full0 + (b * 2 + 0) * 8);
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 12) }
                 if constexpr (NT == 64) {
                     if (grow1) {
-                        MXDSA_WAIT(sm.bar_pv_half[b], bph, 54);
+                        MXDSA_WAIT_POLL(sm.bar_pv_half[b], bph, 54);
                         tc_fence_after();
-                        rescale_o(lane_addr, scale1);
+                        rescale_o(lane_addr + cg * 128, scale1);
                         tc_fence_before();
                     }
                 }
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive_cluster(s_full0 + (b * 2 + 1) * 8);
-                    mbar_arrive(smem_u32(&sm.bar_sc_empty[sc]));
+                    mbar_arrive(smem_u32(&sm.bar_tok_empty[sc]));
                 }
             }
-            // ---------------- end of the pair: combine the halves' l, drain O
+            // ---------------- end of the pair: combine the four partial l of each row, drain O
             if (real_m == -CUDART_INF_F) {
                 l = 0.f;
                 m = -CUDART_INF_F;
             }
-            sm.xl[L] = l;
-            named_bar_sync(1, 128);
-            const float l_tot = l + sm.xl[L ^ 64];
+            sm.xl[kb * 64 + row] = l;
+            named_bar_sync(1, 256);
+            const float l_tot = (sm.xl[row] + sm.xl[64 + row]) + (sm.xl[128 + row] + sm.xl[192 + row]);
             const uint32_t last = gt - 1;
-            MXDSA_WAIT(sm.bar_pv_done[last & 1], (last >> 1) & 1, 55);
+            MXDSA_WAIT_POLL(sm.bar_pv_done[last % kScStages], (last / kScStages) & 1, 55);
             tc_fence_after();
             const int tok_idx = 2 * w.pair + (int)cta;
             const bool store = tok_idx < p.s_q;
@@ -737,7 +908,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             if (!DECODE || !w.split) oscale = __fdividef(1.0f, l_tot + ex2_approx(fmaf(sink, CUDART_L2E_F, -m)));
             else oscale = __fdividef(1.0f, l_tot);
             if (l_tot == 0.f) oscale = 0.f;
-            if (half == 0 && store) {
+            if (kb == 0 && store) {
                 if (!DECODE || !w.split) {
                     float lse = fmaf(m, CUDART_LN2_F, CUDART_LN2_F * lg2_approx(l_tot));
                     if (l_tot == 0.f || lse == -CUDART_INF_F) lse = CUDART_INF_F;
@@ -748,12 +919,13 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     p.lse_accum[((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row] = lg2_approx(l_tot) + m;
                 }
             }
+            const int dim0 = half * 256 + cg * 128;   // this thread's 128 output dims
             if (!DECODE || !w.split) {
-                __nv_bfloat16* dst = p.out + (((long long)w.req * p.s_q + tok_idx) * kHeads + row) * kDim + half * 256;
+                __nv_bfloat16* dst = p.out + (((long long)w.req * p.s_q + tok_idx) * kHeads + row) * kDim + dim0;
 #pragma unroll 1
-                for (int c = 0; c < 256; c += 32) {
+                for (int c = 0; c < 128; c += 32) {
                     float o[32];
-                    tmem_ld32(lane_addr + kColO + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_ld32(lane_addr + kColO + cg * 128 + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
@@ -767,11 +939,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     }
                 }
             } else {
-                float* dst = p.o_accum + (((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row) * kDim + half * 256;
+                float* dst = p.o_accum + (((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row) * kDim + dim0;
 #pragma unroll 1
-                for (int c = 0; c < 256; c += 32) {
+                for (int c = 0; c < 128; c += 32) {
                     float o[32];
-                    tmem_ld32(lane_addr + kColO + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_ld32(lane_addr + kColO + cg * 128 + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
@@ -789,10 +961,22 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 
 done:
     // ------------------------------------------------------------------ tear-down
+    // After a fault, softmax threads leave at different points; one extra arrival per leaving thread
+    // completes the exchange barrier for those still parked on it (they fail their next wait and
+    // follow).  In a normal exit the arrivals are harmless: nobody waits on that barrier any more.
+    if (warp >= 12) named_bar_arrive(1, 256);
     tc_fence_before();
     __syncthreads();
+#ifdef MXDSA_PROFILE
+    if (p.prof != nullptr && blockIdx.x < 2 && blockIdx.y == 0 && threadIdx.x < 64) {
+        if (threadIdx.x == 0) sm.prof[0] = (unsigned long long)(clock64() - prof_kernel_t0);
+        p.prof[blockIdx.x * 64 + threadIdx.x] = sm.prof[threadIdx.x];
+        if (blockIdx.x == 0)
+            for (int i = threadIdx.x; i < 256; i += 64) p.prof[128 + i] = (unsigned long long)((&sm.ev[0][0])[i] - prof_kernel_t0);
+    }
+#endif
     cluster_sync();
-    if (warp == 2) tmem_dealloc<2>(tmem, kTmemCols);
+    if (warp == 10) tmem_dealloc<2>(tmem, kTmemCols);
 }
 
 }  // namespace mxdsa

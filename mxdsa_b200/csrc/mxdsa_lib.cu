@@ -29,6 +29,9 @@ thread_local int tl_last_cuda_error = 0;
     } while (0)
 
 __device__ mxdsa::DeviceFault g_fault;
+#ifdef MXDSA_PROFILE
+__device__ unsigned long long g_prof[384];
+#endif
 
 struct DeviceInfo {
     bool ready = false;
@@ -69,22 +72,6 @@ int device_info(DeviceInfo** out) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// 2-D map over KV rows of 512 bytes; box = one 128-byte chunk of one row (gather4 picks 4 rows).
-int make_kv_map(CUtensorMap* map, const void* base, uint64_t rows) {
-    cuuint64_t dims[2] = {512, rows};
-    cuuint64_t strides[1] = {512};
-    cuuint32_t box[2] = {128, 1};
-    cuuint32_t es[2] = {1, 1};
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, es,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        tl_last_cuda_error = (int)r;
-        return MXDSA_ERR_CUDA;
-    }
-    return MXDSA_OK;
-}
-
 // 5-D map over packed Q: {128 bytes, 64 heads, 4 chunks, tokens, requests}; one box = the 512 data
 // bytes of all 64 heads of one token, landing as [chunk][head][128 B].
 int make_q_map(CUtensorMap* map, const void* base, uint64_t tokens, uint64_t reqs, uint64_t stride_tok,
@@ -119,6 +106,16 @@ int launch_pairs(K kernel, dim3 grid, cudaStream_t stream, const mxdsa::AttnPara
     attr.val.clusterDim = {2, 1, 1};
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
+#ifdef MXDSA_PROFILE
+    {
+        mxdsa::AttnParams ap2 = ap;
+        void* sym = nullptr;
+        MX_CUDA(cudaGetSymbolAddress(&sym, g_prof));
+        ap2.prof = static_cast<unsigned long long*>(sym);
+        MX_CUDA(cudaLaunchKernelEx(&cfg, kernel, ap2, maps));
+        return MXDSA_OK;
+    }
+#endif
     MX_CUDA(cudaLaunchKernelEx(&cfg, kernel, ap, maps));
     return MXDSA_OK;
 }
@@ -293,6 +290,15 @@ int mxdsa_device_fault(void* stream) {
     return MXDSA_OK;
 }
 
+#ifdef MXDSA_PROFILE
+// profiling builds only: copy out the stall counters of cluster 0 ([2][64] cycles)
+int mxdsa_debug_read_prof(unsigned long long* host_out) {
+    MX_CUDA(cudaDeviceSynchronize());
+    MX_CUDA(cudaMemcpyFromSymbol(host_out, g_prof, sizeof(unsigned long long) * 384));
+    return MXDSA_OK;
+}
+#endif
+
 int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     if (p == nullptr || p->q == nullptr || p->kv == nullptr || p->indices == nullptr || p->out == nullptr ||
         p->max_logits == nullptr || p->lse == nullptr)
@@ -326,6 +332,7 @@ int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     ap.fault = d->fault;
     ap.s_kv = p->s_kv;
     ap.num_pairs = p->s_q / 2;
+    ap.kv = static_cast<const uint8_t*>(p->kv);
     ap.kv_scales = static_cast<const uint8_t*>(p->kv) + (size_t)p->s_kv * MXDSA_DIM;
     ap.b = 1;
 
@@ -333,9 +340,6 @@ int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     memset(&maps, 0, sizeof(maps));
     st = make_q_map(&maps.q, p->q, (uint64_t)p->s_q, 1, (uint64_t)p->stride_q_token, (uint64_t)ap.stride_q_b);
     if (st != MXDSA_OK) return st;
-    st = make_kv_map(&maps.kv, p->kv, (uint64_t)p->s_kv);
-    if (st != MXDSA_OK) return st;
-    maps.extra_kv = maps.kv;
 
     const int clusters = ap.num_pairs < d->sm_count / 2 ? ap.num_pairs : d->sm_count / 2;
     const dim3 grid(2 * clusters, 1, 1);
@@ -444,14 +448,6 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
     st = make_q_map(&maps.q, p->q, (uint64_t)p->s_q, (uint64_t)p->b, (uint64_t)p->stride_q_s,
                     p->b > 1 ? (uint64_t)p->stride_q_b : (uint64_t)p->stride_q_s * p->s_q);
     if (st != MXDSA_OK) return st;
-    st = make_kv_map(&maps.kv, p->kv, (uint64_t)p->num_blocks * (uint64_t)ap.rows_per_block);
-    if (st != MXDSA_OK) return st;
-    if (has_extra && p->extra_topk > 0) {
-        st = make_kv_map(&maps.extra_kv, p->extra_kv, (uint64_t)p->extra_num_blocks * (uint64_t)ap.extra_rows_per_block);
-        if (st != MXDSA_OK) return st;
-    } else {
-        maps.extra_kv = maps.kv;
-    }
 
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
     const dim3 grid(2 * ((p->s_q + 1) / 2), p->num_sm_parts, 1);

@@ -5,9 +5,9 @@
 // Conventions
 //  * shared-memory operands are passed as 32-bit shared-window addresses (smem_u32()).
 //  * a tensor-memory address is (lane << 16) | column.
-//  * every wait is bounded: it gives up after `kWaitCycleLimit` SM cycles (or as soon as another
-//    thread of the CTA pair has raised the abort word) and reports failure to the caller, who
-//    leaves through the kernel's normal tear-down.  No trap, no endless spin.
+//  * every wait is bounded: it gives up after about 0.6 s (or as soon as another thread of the
+//    CTA pair has raised the abort word) and reports failure to the caller, who leaves through
+//    the kernel's normal tear-down.  No trap, no endless spin.
 #pragma once
 
 #include <cstdint>
@@ -18,9 +18,6 @@ namespace sm100 {
 
 #define SM100_DEVICE __device__ __forceinline__
 
-// ~0.6 s at 1.9 GHz: far beyond any legitimate wait inside these kernels (the longest is one
-// query pair's main loop, tens of microseconds).
-static constexpr long long kWaitCycleLimit = 1200000000LL;
 
 SM100_DEVICE uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -66,9 +63,12 @@ SM100_DEVICE void fence_mbar_init() {
 SM100_DEVICE void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrival on a barrier of another CTA of the cluster (address from map_to_cta()).  Default
+// semantics (release at CTA scope): what the peer's consumers read is either tensor memory, ordered
+// by tcgen05 fences, or this CTA's own shared memory through the async proxy, ordered by
+// fence.proxy.async -- a cluster-scope release fence per arrival would only cost time.
 SM100_DEVICE void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr)
-                 : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 SM100_DEVICE void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
@@ -103,24 +103,67 @@ SM100_DEVICE bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Blocking flavour: the hardware may suspend the thread for up to `ns` nanoseconds while the phase
+// is pending, so a waiting warp does not compete for issue slots with the warps doing the work.
+SM100_DEVICE bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns, bool cluster_scope) {
+    uint32_t ok;
+    if (cluster_scope)
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(ns)
+            : "memory");
+    else
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(ns)
+            : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  `abort_word` is a shared-memory int that any thread sets when it gives up; all
-// other waiters then leave too.  Returns false when the wait was abandoned.
+// other waiters then leave too.  The wait sleeps in slices of kWaitSliceNs and gives up after
+// kWaitSlices of them (about 0.6 s).  Returns false when the wait was abandoned.
+static constexpr uint32_t kWaitSliceNs = 100000;
+static constexpr int kWaitSlices = 6000;
 SM100_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word,
                             bool cluster_scope = false) {
     if (cluster_scope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < kWaitSlices; ++i) {
+        if (mbar_try_wait_suspend(bar, parity, kWaitSliceNs, cluster_scope)) return true;
+        if (*abort_word != 0) return false;
+    }
+    *abort_word = 1;
+    return false;
+}
+// Polling flavour for latency-critical waiters (a handful of threads per CTA): no suspension, so the
+// waiter resumes within a few cycles of the arrival.  Same ~0.6 s bound, counted in SM cycles.
+SM100_DEVICE bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* abort_word) {
+    if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (true) {
-        if (cluster_scope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))
-            return true;
-        if ((++spins & 63u) == 0) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 255u) == 0) {
             if (*abort_word != 0) return false;
-            if (clock64() - t0 > kWaitCycleLimit) {
+            if (clock64() - t0 > 1200000000LL) {
                 *abort_word = 1;
                 return false;
             }
         }
     }
+}
+SM100_DEVICE void named_bar_arrive(uint32_t id, uint32_t threads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 SM100_DEVICE void fence_proxy_async_smem() {
