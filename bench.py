@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the MXFP8 sparse-attention path.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...        # the CPU arm: torch dequantise-and-gather on host cores
+
+Workload (config.workload): the reference's headline prefill point -- 65 536 query tokens per GPU,
+64 heads, one 512-wide MXFP8 KV head, kv_len 16 384, pair-shared rows of 4096 distinct indices
+(BASELINE config 1; with N GPUs the query pairs are sharded contiguously, KV is replicated and
+nothing is exchanged, so N = 8 is the 524 288-token configuration).  Inputs are synthetic with
+the reference benchmark's distributions (N(0,1) values through the packers); no dataset exists
+for this path.  One "step" = one call of the prefill entry point over the rank's tokens.
+
+Printed JSON (one line, rank 0):
+  value      whole-job MXFP8 TFLOP/s, algorithmic flops 2*s_q*64*topk*(512+512) per step, inputs
+             resident in HBM, CUDA-event time, max over ranks
+  e2e        same metric through the public entry point with HOST buffers: pinned Q / KV / indices
+             copied in and out / lse / max_logits copied back inside the timed region
+  roofline   the attention kernel against the tensor-core roof (see DESIGN.md for the peak used)
+  cpu_baseline  the torch dequantise-and-gather CPU path on a bounded sample (rank 0, N = 1)
+  decode     the reference's decode headline (batch 128, sq 6, main 128 + extra 4096 of 16 384):
+             latency and gathered GB/s against the measured HBM roof (N = 1 only)
+  reference_gpu  the compiled, unmodified reference kernel on the same box and inputs, when
+             oracle/_ref/mxdsa_ext.so is present (N = 1 only)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+S_Q, S_KV, TOPK, HEADS = 65536, 16384, 4096, 64
+METRIC = "prefill sparse-attn MXFP8 TFLOP/s (sq=65536/GPU, kv=16384, topk=4096)"
+
+
+def prefill_flops(s_q: int, topk: int) -> float:
+    return 2.0 * s_q * HEADS * topk * (512 + 512)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        d = json.load(open(path))
+        return dict(source="measured", hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])))
+    return dict(source="fallback", hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v == "Active"})
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm))
+
+
+def make_prefill_inputs(torch, s_q: int, seed: int):
+    from mxdsa_b200 import packing as P
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.empty((s_q, HEADS, 528), dtype=torch.uint8, device="cuda")
+    for i in range(0, s_q, 1024):
+        n = min(1024, s_q - i)
+        q[i:i + n] = P.pack_dual_q64(torch.randn(n, HEADS, 512, device="cuda", generator=g))[0]
+    kvf, w1, w2 = P.make_rank1_kv((S_KV, 1), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    kv = P.pack_dual_prefill_kv64(kvf)[0]
+    idx = torch.empty((s_q // 2, 1, TOPK), dtype=torch.int32, device="cuda")
+    for i in range(0, s_q // 2, 2048):
+        n = min(2048, s_q // 2 - i)
+        idx[i:i + n, 0] = torch.rand(n, S_KV, device="cuda", generator=g).argsort(dim=1)[:, :TOPK].int()
+    return q, kv, idx, w1, w2
+
+
+def time_steps(torch, fn, steps, warmup, dist=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for i in range(steps):
+        fn()
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    return evs[0].elapsed_time(evs[steps]), per
+
+
+def cpu_baseline(torch, q, kv, idx, w1, w2, target_s=12.0):
+    """torch dequantise-and-gather on host cores over a bounded sample of the same workload."""
+    from oracle import cpu_baseline as cb
+    cores = os.cpu_count() or 1
+    k, v = cb.dequant_prefill_kv(kv.cpu(), w1, w2)
+    tokens = 8
+    t0 = time.time()
+    cb.prefill_cpu(q[:tokens].cpu(), k, v, idx[:tokens // 2].cpu(), 512 ** -0.5, cores)
+    probe = max(time.time() - t0, 1e-3)
+    tokens = int(min(2048, max(8, 2 * round(tokens * target_s / probe / 2))))
+    qs, ids = q[:tokens].cpu(), idx[:tokens // 2].cpu()
+    t0 = time.time()
+    cb.prefill_cpu(qs, k, v, ids, 512 ** -0.5, cores)
+    dt = time.time() - t0
+    return dict(value=prefill_flops(tokens, TOPK) / dt / 1e12, unit="TFLOP/s", cores=cores, kind="port",
+                sample=f"{tokens} of {q.shape[0]} query tokens at topk={TOPK}, {dt:.1f} s, torch fp32 "
+                       f"dequantise-and-gather on {cores} threads"), dt
+
+
+def run_reference_arm(args):
+    """The CPU arm.  The reference has no CPU implementation of its kernels; the host-core
+    comparator that its inputs define is the torch dequantise-and-gather path (oracle port)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from mxdsa_b200 import packing as P
+    from oracle import cpu_baseline as cb
+    torch.manual_seed(0)
+    cores = os.cpu_count() or 1
+    tokens = 64
+    q = P.pack_dual_q64(torch.randn(tokens, HEADS, 512))[0]
+    kvf, w1, w2 = P.make_rank1_kv((S_KV, 1))
+    kv = P.pack_dual_prefill_kv64(kvf)[0]
+    idx = torch.stack([torch.randperm(S_KV)[:TOPK] for _ in range(tokens // 2)]).int().view(tokens // 2, 1, TOPK)
+    k, v = cb.dequant_prefill_kv(kv, w1, w2)
+    t0 = time.time()
+    cb.prefill_cpu(q[:8], k, v, idx[:4], 512 ** -0.5, cores)
+    probe = max(time.time() - t0, 1e-3) / 8
+    # bound the whole run to a few minutes: (steps + warmup) * sample_time <= ~120 s
+    budget = 120.0 / max(args.steps + args.warmup, 1)
+    tokens = int(min(tokens, max(2, 2 * int(budget / probe / 2))))
+    fn = lambda: cb.prefill_cpu(q[:tokens], k, v, idx[:tokens // 2], 512 ** -0.5, cores)
+    for _ in range(args.warmup):
+        fn()
+    t0 = time.time()
+    for _ in range(args.steps):
+        fn()
+    dt = (time.time() - t0) / args.steps
+    val = prefill_flops(tokens, TOPK) / dt / 1e12
+    sample = (f"{tokens} query tokens per step at topk={TOPK}, kv_len={S_KV}: torch fp32 dequantise-and-gather "
+              f"(oracle port; the reference ships no CPU implementation) on {cores} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "prefill sq=65536/GPU kv_len=16384 topk=4096 heads=64 dim=512 (bounded sample)",
+                   "sample_tokens": tokens},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def decode_headline(torch, M, peaks, steps, warmup):
+    """batch 128, sq 6, main cache 128 (topk 128) + extra cache 16 384 (topk 4096) per request."""
+    from mxdsa_b200 import packing as P
+    b, s_q, extra = 128, 6, 4096
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = P.pack_dual_q64(torch.randn(b * s_q, HEADS, 512, device="cuda", generator=g))[0].view(b, s_q, HEADS, 528)
+    kvf, w1, w2 = P.make_rank1_kv((2 * b, 64, 1), device="cuda", generator=g)
+    kv = P.pack_dual_decode_kv_pages(kvf)[0]
+    pool = P.pack_dual_decode_kv_pages(torch.randn(256, 64, 1, 512, device="cuda", generator=g))[0]
+    ekv = pool.repeat(b, 1, 1, 1)                      # 128 x 8.65 MB: every request has its own pages
+    off = torch.arange(b, device="cuda", dtype=torch.int32)[:, None, None]
+    idx = (torch.rand(b * s_q, 128, device="cuda", generator=g).argsort(1).int().view(b, s_q, 128) + off * 128)
+    eidx = (torch.rand(b * s_q, 16384, device="cuda", generator=g).argsort(1)[:, :extra].int()
+            .view(b, s_q, extra) + off * 16384).contiguous()
+    sc = 512 ** -0.5
+    first = M.dual_mxfp8_sparse_decode_fwd(q, kv, idx.contiguous(), None, None, None, None, ekv, eidx, None, 512,
+                                           512, sc, w1, w2)
+    meta, splits = first[2], first[3]
+    fn = lambda: M.dual_mxfp8_sparse_decode_fwd(q, kv, idx, None, None, meta, splits, ekv, eidx, None, 512, 512, sc,
+                                                w1, w2)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(steps):
+        flush.zero_()
+        a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(e))
+    ms = statistics.median(ts)
+    pairs = (s_q + 1) // 2
+    gathered = b * pairs * (128 + extra) * 528            # each selected row once per query pair
+    gbs = gathered / ms / 1e6
+    return dict(workload="decode b=128 sq=6 main 128+extra 4096 of 16384", latency_us=ms * 1e3, gathered_bytes=gathered,
+                gbs=gbs, roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
+                                       frac=gbs / peaks["hbm_gbs"], traffic=None),
+                l2_flush="256 MiB written between iterations", launches_per_step=2)
+
+
+def reference_gpu(torch, q, kv, idx, w1, w2, steps, warmup):
+    import importlib.util
+    path = os.path.join(ROOT, "oracle", "_ref", "mxdsa_ext.so")
+    if not os.path.isfile(path):
+        return None
+    try:
+        spec = importlib.util.spec_from_file_location("mxdsa_ext", path)
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+        fn = lambda: ref.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, 512 ** -0.5, w1, w2, None, None)
+        total, per = time_steps(torch, fn, steps, warmup)
+        ms = total / steps
+        return dict(what="unmodified reference kernel (sm_100f build) on the same inputs", ms_per_step=ms,
+                    value=prefill_flops(q.shape[0], TOPK) / ms / 1e9, unit="TFLOP/s")
+    except Exception as ex:  # the comparator is optional
+        return dict(unavailable=repr(ex)[:200])
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--sq", type=int, default=S_Q, help="query tokens per GPU (default: the headline 65536)")
+    ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu baseline, decode and comparator")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import mxdsa_b200 as M
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks = measured_peaks()
+    s_q = args.sq
+    q, kv, idx, w1, w2 = make_prefill_inputs(torch, s_q, seed=100 + rank)   # rank's contiguous shard of pairs
+    sc = 512 ** -0.5
+    fn = lambda: M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, sc, w1, w2, None, None)
+
+    with ClockSampler(local) as clocks:
+        total_ms, per = time_steps(torch, fn, args.steps, args.warmup, dist)
+    M.device_fault()
+    from mxdsa_b200 import sharding
+    job_ms = sharding.max_over_ranks(total_ms)
+    ms_per_step = job_ms / args.steps
+    flops = prefill_flops(s_q, TOPK) * world
+    value = flops / ms_per_step / 1e9
+
+    # roofline of the attention kernel (the only kernel of a prefill step): CUDA events around each
+    # launch on the launching stream; peak = 2 x the measured dense bf16 GEMM rate (MXFP8 runs at
+    # twice the bf16 rate on this part; no MXFP8 GEMM peak is measured on this pool)
+    kern_ms = statistics.median(per)
+    achieved = prefill_flops(s_q, TOPK) / kern_ms / 1e9
+    peak = 2.0 * peaks["bf16_tflops_sustained"]
+    roofline = dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
+                    traffic=None, peak_source=f"2 x {peaks['source']} sustained bf16 GEMM TFLOP/s",
+                    frac_of_nominal_4500=achieved / 4500.0)
+
+    result = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "latency_us": ms_per_step * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8(e4m3+ue8m0)->f32",
+        "data": "synthetic",
+        "config": {"workload": f"prefill sq={s_q}/GPU kv_len={S_KV} topk={TOPK} heads=64 dim=512, query pairs "
+                               f"sharded contiguously over {world} GPU(s), KV replicated, no collective",
+                   "l2": "inputs (Q 2.2 GB, indices 0.5 GB per GPU) are larger than L2; KV (8.65 MB) is L2-resident "
+                         "by design of the workload"},
+        "roofline": roofline, "gpu_launches": args.steps,
+    }
+    if rank == 0:
+        result["clocks"] = clocks.summary()
+
+    if not args.no_extras:
+        # ---- end to end through the public entry point with host buffers
+        hq, hkv, hidx = q.cpu().pin_memory(), kv.cpu().pin_memory(), idx.cpu().pin_memory()
+        h_out = torch.empty((s_q, HEADS, 512), dtype=torch.bfloat16).pin_memory()
+        h_lse = torch.empty((s_q, HEADS), dtype=torch.float32).pin_memory()
+        h_mxl = torch.empty((s_q, HEADS), dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            dq, dkv, didx = hq.cuda(non_blocking=True), hkv.cuda(non_blocking=True), hidx.cuda(non_blocking=True)
+            o, mxl, lse = M.dual_mxfp8_head64_sparse_prefill_fwd(dq, dkv, didx, sc, w1, w2, None, None)
+            h_out.copy_(o, non_blocking=True)
+            h_lse.copy_(lse, non_blocking=True)
+            h_mxl.copy_(mxl, non_blocking=True)
+
+        e_steps = min(args.steps, 3)
+        e_total, _ = time_steps(torch, e2e_step, e_steps, 1, dist)
+        e_ms = sharding.max_over_ranks(e_total) / e_steps
+        result["e2e"] = {"value": flops / e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e_ms,
+                         "h2d_bytes_per_step": hq.numel() + hkv.numel() + hidx.numel() * 4,
+                         "d2h_bytes_per_step": h_out.numel() * 2 + h_lse.numel() * 4 + h_mxl.numel() * 4,
+                         "steps": e_steps}
+        del hq, hidx, h_out
+        if rank == 0 and world == 1:
+            result["cpu_baseline"], _ = cpu_baseline(torch, q, kv, idx, w1, w2)
+            result["reference_gpu"] = reference_gpu(torch, q, kv, idx, w1, w2, min(args.steps, 5), 3)
+            del q, idx
+            torch.cuda.empty_cache()
+            result["decode"] = decode_headline(torch, M, peaks, 20, 5)
+            result["gpu_launches_note"] = "prefill step = 1 attention kernel; decode step = attention + combine"
+    if rank == 0:
+        print(json.dumps(result))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

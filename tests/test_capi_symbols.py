@@ -1,0 +1,55 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol that
+include/mxdsa.h declares; the torch extension module loads and exposes the reference's two names."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "mxdsa.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mxdsa_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = _declared_functions()
+    for n in ("mxdsa_prefill_fwd", "mxdsa_decode_sched", "mxdsa_decode_fwd", "mxdsa_decode_workspace_bytes",
+              "mxdsa_num_sm_parts", "mxdsa_status_string", "mxdsa_last_cuda_error", "mxdsa_device_fault"):
+        assert n in names
+
+
+def test_library_exports_every_declared_symbol():
+    from mxdsa_b200 import capi
+    lib = ctypes.CDLL(capi.LIB_PATH)
+    for name in _declared_functions():
+        assert hasattr(lib, name), name
+    assert set(capi.EXPORTS) <= set(_declared_functions())
+
+
+def test_status_strings_and_argument_checks_need_no_gpu():
+    from mxdsa_b200 import capi
+    L = capi.lib()
+    assert L.mxdsa_status_string(0) == b"ok"
+    assert b"NULL" in L.mxdsa_status_string(1)
+    assert L.mxdsa_prefill_fwd(None) == 1          # MXDSA_ERR_NULL
+    assert L.mxdsa_decode_fwd(None) == 1
+    p = capi.PrefillParams(s_q=3, s_kv=4, topk=64, q=16, kv=16, indices=16, out=16, max_logits=16, lse=16)
+    assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 2   # odd s_q -> MXDSA_ERR_SHAPE
+    p = capi.PrefillParams(s_q=4, s_kv=4, topk=96, q=16, kv=16, indices=16, out=16, max_logits=16, lse=16)
+    assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 2   # topk not a multiple of 64
+    p = capi.PrefillParams(s_q=4, s_kv=4, topk=64, q=24, kv=16, indices=16, out=16, max_logits=16, lse=16,
+                           stride_q_token=64 * 528, stride_indices_pair=64)
+    assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 3   # q not 16-byte aligned -> MXDSA_ERR_ALIGN
+    assert L.mxdsa_decode_workspace_bytes(128, 6, 24) == (128 + 24) * 6 * 64 * 513 * 4
+    assert L.mxdsa_decode_workspace_bytes(0, 6, 24) == 0
+
+
+def test_extension_module_exposes_the_reference_entry_points():
+    import mxdsa_b200
+    ext = mxdsa_b200.ext()
+    assert hasattr(ext, "dual_mxfp8_head64_sparse_prefill_fwd")
+    assert hasattr(ext, "dual_mxfp8_sparse_decode_fwd")
