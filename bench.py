@@ -132,11 +132,12 @@ def cpu_baseline(torch, q, kv, idx, w1, w2, target_s=12.0):
     from oracle import cpu_baseline as cb
     cores = os.cpu_count() or 1
     k, v = cb.dequant_prefill_kv(kv.cpu(), w1, w2)
-    tokens = 8
+    tokens = 32
+    cb.prefill_cpu(q[:tokens].cpu(), k, v, idx[:tokens // 2].cpu(), 512 ** -0.5, cores)   # warm the thread pool
     t0 = time.time()
     cb.prefill_cpu(q[:tokens].cpu(), k, v, idx[:tokens // 2].cpu(), 512 ** -0.5, cores)
     probe = max(time.time() - t0, 1e-3)
-    tokens = int(min(2048, max(8, 2 * round(tokens * target_s / probe / 2))))
+    tokens = int(min(16384, max(32, 2 * round(tokens * target_s / probe / 2))))
     qs, ids = q[:tokens].cpu(), idx[:tokens // 2].cpu()
     t0 = time.time()
     cb.prefill_cpu(qs, k, v, ids, 512 ** -0.5, cores)

@@ -8,7 +8,8 @@ define the uint8 wire format:
                                  num_splits, extra_kv, extra_indices, extra_topk_length,
                                  d_qk, d_v, sm_scale, w1, w2)
 
-They come from the C++ extension module ``lib/mxdsa_ext.so`` (``ext``), which calls the C ABI of
+They come from the C++ extension module ``lib/mxdsa_ext.so`` (``ext``; importable as ``mxdsa_ext``,
+the reference's module name, or as ``mxdsa_b200_ext``), which calls the C ABI of
 ``lib/libmxdsa.so`` (include/mxdsa.h).  ``mxdsa_b200.api`` holds the same two functions written
 against the C ABI with ctypes.  All compute is in the CUDA library; if it has not been built
 (``python -m mxdsa_b200.build``) the first call raises -- there is no fallback path.
@@ -31,7 +32,7 @@ def ext():
         if not os.path.isfile(_EXT_PATH):
             raise RuntimeError(f"{_EXT_PATH} is missing: build it with `python -m mxdsa_b200.build`")
         import torch  # noqa: F401  (libtorch must be loaded before the extension)
-        spec = importlib.util.spec_from_file_location("mxdsa_ext", _EXT_PATH)
+        spec = importlib.util.spec_from_file_location("mxdsa_b200_ext", _EXT_PATH)
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
         _ext = mod

@@ -56,7 +56,6 @@ def build_ext(force: bool = False) -> str:
         troot = os.path.dirname(torch.__file__)
         cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
         cmd = ["c++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DNDEBUG", "-D_GLIBCXX_USE_CXX11_ABI=1",
-               "-DTORCH_EXTENSION_NAME=mxdsa_ext",
                f"-I{os.path.join(HERE, '..', 'include')}", f"-I{cuda_inc}",
                f"-I{os.path.join(troot, 'include')}",
                f"-I{os.path.join(troot, 'include', 'torch', 'csrc', 'api', 'include')}",

@@ -11,22 +11,23 @@
 //   accumulators live in tensor memory: per CTA 128 lanes x (256 O + 2 x 64 P) columns; lane L
 //   holds row L%64, and column half L/64 (P: keys 64*(L/64).., O: dims 256*(L/64)..).
 //
-// Roles (warp-specialised, 20 warps per CTA, 96 registers per thread)
-//   warps 0-3   K producers: read key indices and copy the selected rows of this CTA's 64 keys
+// Roles (warp-specialised, 16 warps per CTA, 128 registers per thread)
+//   warps 0-1   K producers: read key indices and copy the selected rows of this CTA's 64 keys
 //               into a 3-deep K ring with 16-byte cp.async; one warp instruction moves one
 //               512-byte row straight into the 128-byte-swizzled operand layout.  Measured on a
 //               B200 this path sustains ~40 B/clk/SM of random 512-byte rows from L2, against
 //               ~21 B/clk/SM for TMA gather4 issued from the same SM.
-//   warps 4-7   V producers: same for the 256-byte halves of all 128 keys (2-deep V ring)
-//   warp 8      CTA 0: QK issuer for even tiles      CTA 1: relays "K rows landed" to CTA 0
-//   warp 9      CTA 0: QK issuer for odd tiles       (a tcgen05.mma costs one thread ~60 cycles
+//   warps 2-3   V producers: same for the 256-byte halves of all 128 keys (2-deep V ring)
+//   warp 4      CTA 0: QK issuer for even tiles      CTA 1: relays "K rows landed" to CTA 0
+//   warp 5      CTA 0: QK issuer for odd tiles       (a tcgen05.mma costs one thread ~60 cycles
 //               of issue time, so two threads alternate tiles, each with its own P buffer)
-//   warp 10     CTA 0: PV issuer                     CTA 1: relays "V rows landed" to CTA 0
-//   warp 11     operand stager: Q tile TMA + Q scale rows (per pair); K scale rows, key token
+//   warp 6      CTA 0: PV issuer                     CTA 1: relays "V rows landed" to CTA 0
+//   warp 7      operand stager: Q tile TMA + Q scale rows (per pair); K scale rows, key token
 //               scales and validity bits (per tile)
-//   warps 12-19 softmax: P -> registers (each thread one 32-key block of one row), running max
-//               with lazy rescale, exp2, token-scale, per-32-key UE8M0 requantisation to E4M3 S,
-//               O rescale, and the epilogue.
+//   warps 8-15  softmax: two groups of four warps take alternate tiles (each thread one row and one
+//               64-key half of its tile): P -> registers, running max with lazy rescale handed
+//               from group to group, exp2, token-scale, per-32-key UE8M0 requantisation to E4M3
+//               S, O rescale; both groups share the epilogue.
 //
 // Numerical contract (identical to the reference kernels, reference file:line in brackets)
 //   * keys are consumed in numerical tiles of NT = 128 (prefill, topk >= 512) or 64 keys
@@ -62,7 +63,7 @@ static constexpr int kKStages = 3;       // K ring depth (32 KB per stage and CT
 static constexpr int kVStages = 2;       // V ring depth (32 KB per stage and CTA)
 static constexpr int kScStages = 4;      // scale/validity ring depth; also the depth of the
                                          // per-tile "QK done" / "PV done" barrier rings
-static constexpr int kThreads = 640;
+static constexpr int kThreads = 512;
 
 // tensor-memory columns
 static constexpr uint32_t kColO = 0;      // 256 columns
@@ -144,8 +145,9 @@ struct __align__(1024) SmemPlan {
     __align__(128) uint32_t v_sf[2][64 * 4];
     __align__(16) float tok_scale[kScStages][kTileKeys];
     __align__(16) uint32_t valid[kScStages][4];
-    float xmax[2][256];                            // per-row exchange between the four 32-key blocks
-    float xl[256];                                 // partial l exchange at the end of a pair
+    float xmax[2][2][128];                         // [group][tile parity][lane]: row max of the lane's 64 keys
+    float m_pub[2][64];                            // [group][row]: running max after the group's latest tile
+    float xl[256], xr[256];                        // [group*128 + lane]: partial l and true max at the end of a pair
     uint64_t bar_q_landed;                         // local: Q bytes landed
     uint64_t bar_q_full;                           // CTA0: Q data + scale rows of both CTAs ready
     uint64_t bar_q_empty;                          // both: every QK of the pair finished (2 arrivals)
@@ -162,11 +164,12 @@ struct __align__(1024) SmemPlan {
     uint64_t bar_p_empty[2];                       // CTA0: P buffer copied to registers
     uint64_t bar_s_full[2][2];                     // CTA0: [buffer][key half]
     uint64_t bar_o_empty;                          // CTA0: epilogue has drained O
+    uint64_t bar_m_ready[2];                       // local: group g published the running max of its tile
     uint32_t tmem_base;
     int abort_word;
 #ifdef MXDSA_PROFILE
     unsigned long long prof[64];
-    long long ev[16][16];
+    int ev[16][24];
 #endif
 };
 
@@ -321,7 +324,7 @@ __device__ __forceinline__ void rescale_o(uint32_t lane_addr, float f) {
     if (lane == 0) atomicAdd(&sm.prof[(code)], (unsigned long long)(clock64() - prof_t0__));
 // event trace: cycle stamps of tiles 16..31 of this CTA (profiling builds only)
 #define MXDSA_EV(gtile, id) \
-    if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = clock64();
+    if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
 #else
 #define MXDSA_PROF_BEGIN
 #define MXDSA_PROF_END(code)
@@ -372,11 +375,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         mbar_init(smem_u32(&sm.bar_q_full), 2);
         mbar_init(smem_u32(&sm.bar_q_empty), 2);
         for (int i = 0; i < kKStages; ++i) {
-            mbar_init(smem_u32(&sm.bar_k_landed[i]), 128);
+            mbar_init(smem_u32(&sm.bar_k_landed[i]), 64);
             mbar_init(smem_u32(&sm.bar_k_full[i]), 1);
         }
         for (int i = 0; i < kVStages; ++i) {
-            mbar_init(smem_u32(&sm.bar_v_landed[i]), 128);
+            mbar_init(smem_u32(&sm.bar_v_landed[i]), 64);
             mbar_init(smem_u32(&sm.bar_v_full[i]), 1);
         }
         for (int i = 0; i < kScStages; ++i) {
@@ -384,15 +387,17 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             mbar_init(smem_u32(&sm.bar_pv_done[i]), 1);
             mbar_init(smem_u32(&sm.bar_sc_full[i]), 2);
             mbar_init(smem_u32(&sm.bar_tok_full[i]), 1);
-            mbar_init(smem_u32(&sm.bar_tok_empty[i]), 8);
+            mbar_init(smem_u32(&sm.bar_tok_empty[i]), 4);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&sm.bar_p_empty[i]), 16);
-            mbar_init(smem_u32(&sm.bar_s_full[i][0]), 16);
-            mbar_init(smem_u32(&sm.bar_s_full[i][1]), 16);
+            mbar_init(smem_u32(&sm.bar_p_empty[i]), 8);
+            mbar_init(smem_u32(&sm.bar_s_full[i][0]), 8);
+            mbar_init(smem_u32(&sm.bar_s_full[i][1]), 8);
             mbar_init(smem_u32(&sm.bar_pv_half[i]), 1);
         }
         mbar_init(smem_u32(&sm.bar_o_empty), 16);
+        mbar_init(smem_u32(&sm.bar_m_ready[0]), 4);
+        mbar_init(smem_u32(&sm.bar_m_ready[1]), 4);
         sm.abort_word = 0;
 #ifdef MXDSA_PROFILE
         for (int i = 0; i < 64; ++i) sm.prof[i] = 0;
@@ -402,7 +407,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #ifdef MXDSA_PROFILE
     const long long prof_kernel_t0 = clock64();
 #endif
-    if (warp == 11) {
+    if (warp == 7) {
         // V dimension scales: rows 0-31 feed lane quadrants 0,1 (dims of CTA 0 = w1), rows 32-63
         // quadrants 2,3 (dims of CTA 1 = w2); every row of a group is the same four words.
         for (int i = lane; i < 64; i += 32) {
@@ -417,7 +422,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     }
     __syncthreads();
     cluster_sync();
-    if (warp == 10) {
+    if (warp == 6) {
         tmem_alloc<2>(smem_u32(&sm.tmem_base), kTmemCols);
         tmem_relinquish<2>();
     }
@@ -432,9 +437,9 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     const uint64_t desc_sf = smem_desc_base(0, 128, 0);       // scale rows, 16 bytes each
 
     // ------------------------------------------------------------------ roles
-    if (warp < 4) {
-        // ===================== K producers (warps 0-3) =====================
-        // keys 64*cta + 16*warp + i (i < 16) of the tile, whole 512-byte rows, one per instruction;
+    if (warp < 2) {
+        // ===================== K producers (warps 0-1) =====================
+        // keys 64*cta + 32*warp + i (i < 32) of the tile, whole 512-byte rows, one per instruction;
         // lane L writes byte chunk L of the row -> chunk tile L/8, 16-byte column (L%8) ^ (row%8).
         WorkIter<DECODE> it(p);
         WorkItem w;
@@ -442,12 +447,12 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-            const int key = 64 * (int)cta + 16 * warp + (lane & 15);
+            const int key = 64 * (int)cta + 32 * warp + lane;
             bool valid;
             const uint8_t* slot;
             const uint8_t* ptr = key_lookup<DECODE>(p, w, w.blk_begin + key / 64, key % 64, valid, slot);
             for (int t = 0; t < ntiles; ++t, ++gt) {
-                const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
+                const uint32_t s = gt % kKStages;
                 const uint8_t* ptr_next = nullptr;
                 if (t + 1 < ntiles)   // prefetch the next tile's row addresses
                     ptr_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + key / 64, key % 64, valid, slot);
@@ -457,11 +462,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 }
                 if (warp == 0 && lane == 0) { MXDSA_EV(gt, 0) }
                 const uint32_t kbase = smem_u32(sm.k[s]) + (lane / 8) * 8192;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
+#pragma unroll 8
+                for (int i = 0; i < 32; ++i) {
                     const uint8_t* src = reinterpret_cast<const uint8_t*>(
                         __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), i));
-                    const int r = 16 * warp + i;
+                    const int r = 32 * warp + i;
                     cp_async16(kbase + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + lane * 16 : p.kv,
                                src ? 16u : 0u);
                 }
@@ -470,50 +475,54 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 ptr = ptr_next;
             }
         }
-    } else if (warp < 8) {
-        // ===================== V producers (warps 4-7) =====================
-        // keys 32*pw + 2i, 2i+1 (i < 16), bytes 256*cta .. +255, two keys per instruction;
+    } else if (warp < 4) {
+        // ===================== V producers (warps 2-3) =====================
+        // keys 64*pw + j (j < 64), bytes 256*cta .. +255, two keys per instruction;
         // lane L writes chunk tile (L%16)/8 of key 2i + L/16.
-        const int pw = warp - 4;
+        const int pw = warp - 2;
         WorkIter<DECODE> it(p);
         WorkItem w;
         uint32_t gt = 0;
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-            const int key = 32 * pw + lane;
             bool valid;
             const uint8_t* slot;
-            const uint8_t* ptr = key_lookup<DECODE>(p, w, w.blk_begin + key / 64, key % 64, valid, slot);
+            // block pw of the tile: lane L looks up keys L and 32+L of that block
+            const uint8_t* pa = key_lookup<DECODE>(p, w, w.blk_begin + pw, lane, valid, slot);
+            const uint8_t* pb = key_lookup<DECODE>(p, w, w.blk_begin + pw, 32 + lane, valid, slot);
             for (int t = 0; t < ntiles; ++t, ++gt) {
-                const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
-                const uint8_t* ptr_next = nullptr;
-                if (t + 1 < ntiles)
-                    ptr_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + key / 64, key % 64, valid, slot);
+                const uint32_t s = gt % kVStages;
+                const uint8_t *pa_next = nullptr, *pb_next = nullptr;
+                if (t + 1 < ntiles) {
+                    pa_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + pw, lane, valid, slot);
+                    pb_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + pw, 32 + lane, valid, slot);
+                }
                 if (gt >= kVStages) {   // stage s was last used by tile gt-2
                     const uint32_t g = gt - kVStages;
                     MXDSA_WAIT(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 11);
                 }
                 if (pw == 0 && lane == 0) { MXDSA_EV(gt, 2) }
                 const uint32_t vbase = smem_u32(sm.v[s]) + ((lane & 15) / 8) * 16384;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint8_t* src = reinterpret_cast<const uint8_t*>(
-                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), 2 * i + lane / 16));
-                    const int r = 32 * pw + 2 * i + lane / 16;
+#pragma unroll 8
+                for (int i = 0; i < 32; ++i) {
+                    const unsigned long long pp = reinterpret_cast<unsigned long long>(i < 16 ? pa : pb);
+                    const uint8_t* src =
+                        reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, pp, (2 * i + lane / 16) & 31));
+                    const int r = 64 * pw + 2 * i + lane / 16;
                     cp_async16(vbase + r * 128 + (((lane & 7) ^ (r & 7)) << 4),
                                src ? src + 256 * cta + (lane & 15) * 16 : p.kv, src ? 16u : 0u);
                 }
                 cp_async_arrive(smem_u32(&sm.bar_v_landed[s]));
                 if (pw == 0 && lane == 0) { MXDSA_EV(gt, 3) }
-                ptr = ptr_next;
-                (void)ph;
+                pa = pa_next;
+                pb = pb_next;
             }
         }
-    } else if (warp == 8 || warp == 9) {
+    } else if (warp == 4 || warp == 5) {
         if (cta == 0 && lane == 0) {
             // ===================== QK issuers (CTA 0): warp 8 even tiles, warp 9 odd tiles ==========
-            const uint32_t e = warp - 8;   // tile parity = P buffer = scale column set owned by this issuer
+            const uint32_t e = warp - 4;   // tile parity = P buffer = scale column set owned by this issuer
             WorkIter<DECODE> it(p);
             WorkItem w;
             uint32_t gt = 0, gw = 0;
@@ -570,7 +579,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 }
                 ++gw;
             }
-        } else if (cta == 1 && warp == 8 && lane == 0) {
+        } else if (cta == 1 && warp == 4 && lane == 0) {
             // ===================== K relay (CTA 1) =====================
             WorkIter<DECODE> it(p);
             WorkItem w;
@@ -587,7 +596,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 }
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 6) {
         if (cta == 0 && lane == 0) {
             // ===================== PV issuer (CTA 0) =====================
             WorkIter<DECODE> it(p);
@@ -658,7 +667,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 }
             }
         }
-    } else if (warp == 11) {
+    } else if (warp == 7) {
         // ===================== operand stager =====================
         WorkIter<DECODE> it(p);
         WorkItem w;
@@ -730,16 +739,17 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             ++gw;
         }
     } else {
-        // ===================== softmax + epilogue (warps 12-19) =====================
-        // Two warps share each tensor-memory lane quadrant: warp w works on lanes 32*(w%4).. and on
-        // 32-column group cg = (w-12)/4 of the lane's 64 P columns, i.e. on ONE 32-key block of the
-        // tile (block kb = 2*half + cg), which is also one UE8M0 scale group of S.
+        // ===================== softmax + epilogue (warps 8-15) =====================
+        // Two groups of four warps take alternate tiles (group = tile parity = P buffer), so one
+        // group's exp / quantise / store phase overlaps the other group's load / max phase.  Inside a
+        // group a thread owns one row and one 64-key half of the tile (two UE8M0 scale groups of S).
+        // The only serial link between consecutive tiles is the running maximum: after deciding m_t a
+        // group publishes it (sm.m_pub) and the other group picks it up before deciding m_{t+1}.
+        const int grp = (warp - 8) >> 2;
         const int q4 = warp & 3;                 // lane quadrant of tensor memory
-        const int cg = (warp - 12) >> 2;         // column group inside the lane
         const int L = q4 * 32 + lane;            // tensor-memory lane
         const int row = L % 64;                  // head
         const int half = L / 64;                 // key half of a tile / dim half of O
-        const int kb = 2 * half + cg;            // 32-key block of the tile handled by this thread
         const uint32_t lane_addr = tmem + (uint32_t(q4 * 32) << 16);
         const uint32_t p_empty0 = map_to_cta(smem_u32(&sm.bar_p_empty[0]), 0);
         const uint32_t s_full0 = map_to_cta(smem_u32(&sm.bar_s_full[0][0]), 0);
@@ -747,140 +757,173 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         WorkIter<DECODE> it(p);
         WorkItem w;
-        uint32_t gt = 0;
+        uint32_t gt = 0, gw = 0;
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-            float m = -1e30f, l = 0.f, real_m = -CUDART_INF_F;
+            float m_own = -1e30f;   // running max after this group's latest tile of the pair
+            float l = 0.f, real_m = -CUDART_INF_F;
             for (int t = 0; t < ntiles; ++t, ++gt) {
+                if ((int)(gt & 1) != grp) continue;
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
-                const uint32_t b = gt & 1, bph = (gt >> 1) & 1;
+                const uint32_t b = grp, bph = (gt >> 1) & 1;
                 MXDSA_WAIT_POLL(sm.bar_tok_full[sc], sph, 50);
-                const uint32_t vmask = sm.valid[sc][kb];
+                const uint32_t v0 = sm.valid[sc][2 * half], v1 = sm.valid[sc][2 * half + 1];
                 MXDSA_WAIT_POLL(sm.bar_qk_done[sc], sph, 51);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 8) }
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 8) }
                 tc_fence_after();
-                float x[32];
-                tmem_ld32(lane_addr + kColP + b * 64 + cg * 32, reinterpret_cast<uint32_t*>(x));
+                float x[64];
+                tmem_ld32(lane_addr + kColP + b * 64, reinterpret_cast<uint32_t*>(x));
+                tmem_ld32(lane_addr + kColP + b * 64 + 32, reinterpret_cast<uint32_t*>(x + 32));
                 tmem_wait_ld();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(p_empty0 + b * 8);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 9) }
-                if (vmask != 0xffffffffu) {
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 9) }
+                if ((v0 & v1) != 0xffffffffu) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) x[i] = ((vmask >> i) & 1u) ? x[i] : -CUDART_INF_F;
+                    for (int i = 0; i < 64; ++i) x[i] = (((i < 32 ? v0 : v1) >> (i & 31)) & 1u) ? x[i] : -CUDART_INF_F;
                 }
-                float mx4[4] = {x[0], x[1], x[2], x[3]};
+                float mx8[8];
 #pragma unroll
-                for (int i = 4; i < 32; i += 4) {
-                    mx4[0] = fmaxf(mx4[0], x[i]);
-                    mx4[1] = fmaxf(mx4[1], x[i + 1]);
-                    mx4[2] = fmaxf(mx4[2], x[i + 2]);
-                    mx4[3] = fmaxf(mx4[3], x[i + 3]);
+                for (int i = 0; i < 8; ++i) mx8[i] = x[i];
+#pragma unroll
+                for (int i = 8; i < 64; i += 8) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) mx8[j] = fmaxf(mx8[j], x[i + j]);
                 }
-                const float own_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-                float* xm = sm.xmax[gt & 1];
-                xm[kb * 64 + row] = own_max;
-                named_bar_sync(1, 256);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 10) }
-                const float t0 = fmaxf(xm[row], xm[64 + row]);          // key half 0 (blocks 0, 1)
-                const float t1 = fmaxf(xm[128 + row], xm[192 + row]);   // key half 1 (blocks 2, 3)
+                const float own_max = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                            fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * p.scale_log2;
+                float* xm = sm.xmax[grp][bph];
+                xm[L] = own_max;
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 16) }
+                named_bar_sync(1 + grp, 128);
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 17) }
+                const float peer_max = xm[L ^ 64];
+                // the running maximum handed over by the other group (value ignored on a pair's first
+                // tile, but every phase of that barrier is observed)
+                if (gt > 0) MXDSA_WAIT_POLL(sm.bar_m_ready[grp ^ 1], ((gt - 1) >> 1) & 1, 58);
+                const float m_prev = t == 0 ? -1e30f : sm.m_pub[grp ^ 1][row];
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 10) }
+                const float sprev = (m_own == m_prev) ? 1.f : ex2_approx(m_own - m_prev);
                 // numerical tiles: NT = 128 -> one per tensor-core tile; NT = 64 -> key half 0 then 1
                 float m_used, scale0 = 1.f, scale1 = 1.f;
                 bool grow0, grow1 = false;
                 if constexpr (NT == 128) {
-                    const float tmax = fmaxf(t0, t1);
+                    const float tmax = fmaxf(own_max, peer_max);
                     real_m = fmaxf(real_m, tmax);
-                    grow0 = __any_sync(0xffffffffu, tmax - m > 6.0f);
-                    const float nm = grow0 ? fmaxf(m, tmax) : m;
-                    scale0 = grow0 ? ex2_approx(m - nm) : 1.f;
-                    m = nm;
-                    m_used = m;
+                    grow0 = __any_sync(0xffffffffu, tmax - m_prev > 6.0f);
+                    const float nm = grow0 ? fmaxf(m_prev, tmax) : m_prev;
+                    scale0 = grow0 ? ex2_approx(m_prev - nm) : 1.f;
+                    m_own = nm;
+                    m_used = nm;
                 } else {
+                    const float t0 = half == 0 ? own_max : peer_max;
+                    const float t1 = half == 0 ? peer_max : own_max;
                     real_m = fmaxf(real_m, fmaxf(t0, t1));
-                    grow0 = __any_sync(0xffffffffu, t0 - m > 6.0f);
-                    const float m1 = grow0 ? fmaxf(m, t0) : m;
-                    scale0 = grow0 ? ex2_approx(m - m1) : 1.f;
+                    grow0 = __any_sync(0xffffffffu, t0 - m_prev > 6.0f);
+                    const float m1 = grow0 ? fmaxf(m_prev, t0) : m_prev;
+                    scale0 = grow0 ? ex2_approx(m_prev - m1) : 1.f;
                     grow1 = __any_sync(0xffffffffu, t1 - m1 > 6.0f);
                     const float m2 = grow1 ? fmaxf(m1, t1) : m1;
                     scale1 = grow1 ? ex2_approx(m1 - m2) : 1.f;
                     m_used = half == 0 ? m1 : m2;
-                    m = m2;
+                    m_own = m2;
                 }
-                // probabilities, key-scaled, re-quantised (this thread = one 32-key scale group)
+                sm.m_pub[grp][row] = m_own;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sm.bar_m_ready[grp]));
+                // probabilities, key-scaled, re-quantised per 32 keys
                 const float2 negm2 = make_float2(-m_used, -m_used);
-                const float4* tok4 = reinterpret_cast<const float4*>(&sm.tok_scale[sc][kb * 32]);
+                const float4* tok4 = reinterpret_cast<const float4*>(&sm.tok_scale[sc][half * 64]);
                 float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-                float am4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t s8[16];
+                uint32_t e_bytes = 0;
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    const float4 tk = tok4[i / 4];
-                    float2 a = f2_fma(make_float2(x[i], x[i + 1]), scale2, negm2);
-                    float2 c = f2_fma(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
-                    a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
-                    c = make_float2(ex2_approx(c.x), ex2_approx(c.y));
-                    sum2[0] = f2_add(sum2[0], a);
-                    sum2[1] = f2_add(sum2[1], c);
-                    a = f2_mul(a, make_float2(tk.x, tk.y));
-                    c = f2_mul(c, make_float2(tk.z, tk.w));
-                    am4[0] = fmaxf(am4[0], a.x);
-                    am4[1] = fmaxf(am4[1], a.y);
-                    am4[2] = fmaxf(am4[2], c.x);
-                    am4[3] = fmaxf(am4[3], c.y);
-                    x[i] = a.x; x[i + 1] = a.y; x[i + 2] = c.x; x[i + 3] = c.y;
+                for (int g = 0; g < 2; ++g) {
+                    float am4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int i = 32 * g; i < 32 * g + 32; i += 4) {
+#ifdef MXDSA_EXP_NOTOK
+                        const float4 tk = make_float4(1.f, 1.f, 1.f, 1.f);
+                        (void)tok4;
+#else
+                        const float4 tk = tok4[i / 4];
+#endif
+                        float2 a = f2_fma(make_float2(x[i], x[i + 1]), scale2, negm2);
+                        float2 c = f2_fma(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
+                        a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
+                        c = make_float2(ex2_approx(c.x), ex2_approx(c.y));
+                        sum2[0] = f2_add(sum2[0], a);
+                        sum2[1] = f2_add(sum2[1], c);
+                        a = f2_mul(a, make_float2(tk.x, tk.y));
+                        c = f2_mul(c, make_float2(tk.z, tk.w));
+                        am4[0] = fmaxf(am4[0], a.x);
+                        am4[1] = fmaxf(am4[1], a.y);
+                        am4[2] = fmaxf(am4[2], c.x);
+                        am4[3] = fmaxf(am4[3], c.y);
+                        x[i] = a.x; x[i + 1] = a.y; x[i + 2] = c.x; x[i + 3] = c.y;
+                    }
+                    const float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
+                    uint32_t e = cvt_ue8m0_roundup(amax > 0.f ? __fdividef(amax, 448.0f) : 1.0f);
+                    e = max(e, 61u);
+                    e_bytes |= e << (8 * g);
+                    const float mulf = __uint_as_float((254u - e) << 23);
+                    const float2 mul2 = make_float2(mulf, mulf);
+                    if (g == 0 && warp == 8 && lane == 0) { MXDSA_EV(gt, 18) }
+#pragma unroll
+                    for (int i = 32 * g; i < 32 * g + 32; i += 4) {
+                        const float2 a = f2_mul(make_float2(x[i], x[i + 1]), mul2);
+                        const float2 c = f2_mul(make_float2(x[i + 2], x[i + 3]), mul2);
+                        s8[i / 4] = (uint32_t)cvt_e4m3x2(a.x, a.y) | ((uint32_t)cvt_e4m3x2(c.x, c.y) << 16);
+                    }
                 }
-                const float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
                 const float2 s2 = f2_add(sum2[0], sum2[1]);
                 const float sum = s2.x + s2.y;
-                uint32_t e = cvt_ue8m0_roundup(amax > 0.f ? __fdividef(amax, 448.0f) : 1.0f);
-                e = max(e, 61u);
-                const float mulf = __uint_as_float((254u - e) << 23);
-                const float2 mul2 = make_float2(mulf, mulf);
-                uint32_t s8[8];
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    const float2 a = f2_mul(make_float2(x[i], x[i + 1]), mul2);
-                    const float2 c = f2_mul(make_float2(x[i + 2], x[i + 3]), mul2);
-                    s8[i / 4] = (uint32_t)cvt_e4m3x2(a.x, a.y) | ((uint32_t)cvt_e4m3x2(c.x, c.y) << 16);
-                }
-                // l bookkeeping: every m update rescales all partial sums of the row
+                // l bookkeeping: every update of m rescales all partial sums of the row
                 if constexpr (NT == 128) {
-                    l = fmaf(l, scale0, sum);
+                    l = fmaf(l * sprev, scale0, sum);
                 } else {
-                    if (half == 0) l = fmaf(l, scale0, sum) * scale1;
-                    else l = fmaf(l * scale0, scale1, sum);
+                    if (half == 0) l = fmaf(l * sprev, scale0, sum) * scale1;
+                    else l = fmaf(l * sprev * scale0, scale1, sum);
                 }
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 11) }
                 // S buffer b is free once the PV of tile gt-2 has finished
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 11) }
                 if (gt >= 2) {
                     const uint32_t g = gt - 2;
                     MXDSA_WAIT_POLL(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 52);
                 }
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 19) }
                 {
                     uint8_t* srow = sm.s[b];
-                    *reinterpret_cast<uint4*>(srow + swz128(row, kb * 32)) = make_uint4(s8[0], s8[1], s8[2], s8[3]);
-                    *reinterpret_cast<uint4*>(srow + swz128(row, kb * 32 + 16)) = make_uint4(s8[4], s8[5], s8[6], s8[7]);
-                    // scale rows: row (row%32) and its copy at +32; word row/32; byte kb
-                    reinterpret_cast<uint8_t*>(&sm.s_sf[b][(row % 32) * 4 + row / 32])[kb] = (uint8_t)e;
-                    reinterpret_cast<uint8_t*>(&sm.s_sf[b][(32 + row % 32) * 4 + row / 32])[kb] = (uint8_t)e;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + i * 16)) =
+                            make_uint4(s8[4 * i], s8[4 * i + 1], s8[4 * i + 2], s8[4 * i + 3]);
+                    // scale rows: row (row%32) and its copy at +32; word row/32; bytes 2*half, 2*half+1
+                    reinterpret_cast<uint16_t*>(&sm.s_sf[b][(row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
+                    reinterpret_cast<uint16_t*>(&sm.s_sf[b][(32 + row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
                 }
-                // O rescale before the first key half is accumulated (this thread: 128 of the lane's columns)
+                // O rescale before the first key half is accumulated (this thread: its whole lane)
                 if (grow0 && t > 0) {
                     MXDSA_WAIT_POLL(sm.bar_pv_done[(gt - 1) % kScStages], ((gt - 1) / kScStages) & 1, 53);
                     tc_fence_after();
-                    rescale_o(lane_addr + cg * 128, scale0);
+                    rescale_o(lane_addr, scale0);
+                    rescale_o(lane_addr + 128, scale0);
                     tc_fence_before();
                 }
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 20) }
                 fence_proxy_async_smem();
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 21) }
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(s_full0 + (b * 2 + 0) * 8);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 12) }
+                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 12) }
                 if constexpr (NT == 64) {
                     if (grow1) {
                         MXDSA_WAIT_POLL(sm.bar_pv_half[b], bph, 54);
                         tc_fence_after();
-                        rescale_o(lane_addr + cg * 128, scale1);
+                        rescale_o(lane_addr, scale1);
+                        rescale_o(lane_addr + 128, scale1);
                         tc_fence_before();
                     }
                 }
@@ -890,15 +933,27 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     mbar_arrive(smem_u32(&sm.bar_tok_empty[sc]));
                 }
             }
-            // ---------------- end of the pair: combine the four partial l of each row, drain O
-            if (real_m == -CUDART_INF_F) {
-                l = 0.f;
+            // ---------------- end of the pair: final m, the four partial l of each row, drain O
+            const uint32_t last = gt - 1;
+            float m_fin = m_own;
+            if ((int)(last & 1) != grp) {
+                MXDSA_WAIT_POLL(sm.bar_m_ready[grp ^ 1], (last >> 1) & 1, 59);
+                m_fin = sm.m_pub[grp ^ 1][row];
+                l *= (m_own == m_fin) ? 1.f : ex2_approx(m_own - m_fin);
+            }
+            sm.xl[grp * 128 + L] = l;
+            sm.xr[grp * 128 + L] = real_m;
+            named_bar_sync(3, 256);
+            const float* xl = sm.xl;
+            const float* xr = sm.xr;
+            float l_tot = (xl[row] + xl[64 + row]) + (xl[128 + row] + xl[192 + row]);
+            const float real_all = fmaxf(fmaxf(xr[row], xr[64 + row]), fmaxf(xr[128 + row], xr[192 + row]));
+            named_bar_sync(3, 256);   // everybody has read the exchange area before the next pair writes it
+            float m = m_fin;
+            if (real_all == -CUDART_INF_F) {
+                l_tot = 0.f;
                 m = -CUDART_INF_F;
             }
-            sm.xl[kb * 64 + row] = l;
-            named_bar_sync(1, 256);
-            const float l_tot = (sm.xl[row] + sm.xl[64 + row]) + (sm.xl[128 + row] + sm.xl[192 + row]);
-            const uint32_t last = gt - 1;
             MXDSA_WAIT_POLL(sm.bar_pv_done[last % kScStages], (last / kScStages) & 1, 55);
             tc_fence_after();
             const int tok_idx = 2 * w.pair + (int)cta;
@@ -908,24 +963,24 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             if (!DECODE || !w.split) oscale = __fdividef(1.0f, l_tot + ex2_approx(fmaf(sink, CUDART_L2E_F, -m)));
             else oscale = __fdividef(1.0f, l_tot);
             if (l_tot == 0.f) oscale = 0.f;
-            if (kb == 0 && store) {
+            if (grp == 0 && half == 0 && store) {
                 if (!DECODE || !w.split) {
                     float lse = fmaf(m, CUDART_LN2_F, CUDART_LN2_F * lg2_approx(l_tot));
                     if (l_tot == 0.f || lse == -CUDART_INF_F) lse = CUDART_INF_F;
                     const long long o = ((long long)w.req * p.s_q + tok_idx) * kHeads + row;
                     p.lse[o] = lse;
-                    if (!DECODE) p.max_logits[o] = real_m * CUDART_LN2_F;
+                    if (!DECODE) p.max_logits[o] = real_all * CUDART_LN2_F;
                 } else {
                     p.lse_accum[((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row] = lg2_approx(l_tot) + m;
                 }
             }
-            const int dim0 = half * 256 + cg * 128;   // this thread's 128 output dims
+            const int dim0 = half * 256 + grp * 128;   // this thread's 128 output dims
             if (!DECODE || !w.split) {
                 __nv_bfloat16* dst = p.out + (((long long)w.req * p.s_q + tok_idx) * kHeads + row) * kDim + dim0;
 #pragma unroll 1
                 for (int c = 0; c < 128; c += 32) {
                     float o[32];
-                    tmem_ld32(lane_addr + kColO + cg * 128 + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_ld32(lane_addr + kColO + grp * 128 + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
@@ -943,7 +998,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #pragma unroll 1
                 for (int c = 0; c < 128; c += 32) {
                     float o[32];
-                    tmem_ld32(lane_addr + kColO + cg * 128 + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_ld32(lane_addr + kColO + grp * 128 + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
@@ -956,6 +1011,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(o_empty0);
+            ++gw;
         }
     }
 
@@ -964,7 +1020,10 @@ done:
     // After a fault, softmax threads leave at different points; one extra arrival per leaving thread
     // completes the exchange barrier for those still parked on it (they fail their next wait and
     // follow).  In a normal exit the arrivals are harmless: nobody waits on that barrier any more.
-    if (warp >= 12) named_bar_arrive(1, 256);
+    if (warp >= 8) {
+        named_bar_arrive(1 + ((warp - 8) >> 2), 128);
+        named_bar_arrive(3, 256);
+    }
     tc_fence_before();
     __syncthreads();
 #ifdef MXDSA_PROFILE
@@ -972,11 +1031,11 @@ done:
         if (threadIdx.x == 0) sm.prof[0] = (unsigned long long)(clock64() - prof_kernel_t0);
         p.prof[blockIdx.x * 64 + threadIdx.x] = sm.prof[threadIdx.x];
         if (blockIdx.x == 0)
-            for (int i = threadIdx.x; i < 256; i += 64) p.prof[128 + i] = (unsigned long long)((&sm.ev[0][0])[i] - prof_kernel_t0);
+            for (int i = threadIdx.x; i < 384; i += 64) p.prof[128 + i] = (unsigned long long)(unsigned)(&sm.ev[0][0])[i];
     }
 #endif
     cluster_sync();
-    if (warp == 10) tmem_dealloc<2>(tmem, kTmemCols);
+    if (warp == 6) tmem_dealloc<2>(tmem, kTmemCols);
 }
 
 }  // namespace mxdsa

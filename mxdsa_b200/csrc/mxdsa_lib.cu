@@ -30,7 +30,7 @@ thread_local int tl_last_cuda_error = 0;
 
 __device__ mxdsa::DeviceFault g_fault;
 #ifdef MXDSA_PROFILE
-__device__ unsigned long long g_prof[384];
+__device__ unsigned long long g_prof[512];
 #endif
 
 struct DeviceInfo {
@@ -294,7 +294,7 @@ int mxdsa_device_fault(void* stream) {
 // profiling builds only: copy out the stall counters of cluster 0 ([2][64] cycles)
 int mxdsa_debug_read_prof(unsigned long long* host_out) {
     MX_CUDA(cudaDeviceSynchronize());
-    MX_CUDA(cudaMemcpyFromSymbol(host_out, g_prof, sizeof(unsigned long long) * 384));
+    MX_CUDA(cudaMemcpyFromSymbol(host_out, g_prof, sizeof(unsigned long long) * 512));
     return MXDSA_OK;
 }
 #endif

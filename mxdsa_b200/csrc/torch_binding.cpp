@@ -248,8 +248,14 @@ void device_fault() {
 
 }  // namespace
 
-PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+static void define_module(pybind11::module_& m) {
     m.def("dual_mxfp8_head64_sparse_prefill_fwd", &prefill_fwd);
     m.def("dual_mxfp8_sparse_decode_fwd", &decode_fwd);
     m.def("device_fault", &device_fault);
 }
+
+// Two import names for the same shared object: `mxdsa_ext` is the reference's module name (drop-in
+// for callers that load the file by path under that name); `mxdsa_b200_ext` is what the Python
+// package uses, so that it can live in one process with the reference's own extension.
+PYBIND11_MODULE(mxdsa_ext, m) { define_module(m); }
+PYBIND11_MODULE(mxdsa_b200_ext, m) { define_module(m); }

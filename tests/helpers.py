@@ -46,3 +46,18 @@ def check_against_golden(g, out, lse, max_logits=None, lse_is_b_h_s=False, out_t
         assert np.array_equal(np.isneginf(max_logits), np.isneginf(gm)), "max_logits -inf pattern"
         fin = np.isfinite(gm)
         assert np.abs(max_logits[fin] - gm[fin]).max(initial=0.0) <= LSE_MAX_ABS
+
+
+def check_against_oracle(out, ref):
+    """CUDA result against the CPU oracle (level 1).  The oracle evaluates exp2 exactly while the
+    kernel uses ex2.approx, so a probability that sits on an E4M3 rounding boundary can round the
+    other way: isolated elements then differ by one E4M3 step of that probability times |V|.  The
+    strict 2e-2 bound is applied against the reference KERNEL (golden fixtures); against the
+    oracle we require the same bound for all but a vanishing fraction of elements."""
+    from oracle import mxdsa_oracle as O
+    out = np.asarray(out, np.float64)
+    ref = np.asarray(ref, np.float64)
+    d = np.abs(out - ref)
+    assert O.cosine(out, ref) >= 0.99999, ("cosine", O.cosine(out, ref))
+    assert (d > OUT_MAX_ABS).mean() <= 2e-4, ("fraction beyond 2e-2", (d > OUT_MAX_ABS).mean())
+    assert d.max() <= 0.5, ("max-abs", d.max())

@@ -53,3 +53,9 @@ def test_extension_module_exposes_the_reference_entry_points():
     ext = mxdsa_b200.ext()
     assert hasattr(ext, "dual_mxfp8_head64_sparse_prefill_fwd")
     assert hasattr(ext, "dual_mxfp8_sparse_decode_fwd")
+    # the same file is importable under the reference's module name
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("mxdsa_ext", mxdsa_b200._EXT_PATH)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert hasattr(mod, "dual_mxfp8_head64_sparse_prefill_fwd") and hasattr(mod, "dual_mxfp8_sparse_decode_fwd")
