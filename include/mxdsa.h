@@ -154,6 +154,27 @@ typedef struct mxdsa_decode_params {
 
 int mxdsa_decode_fwd(const mxdsa_decode_params* p);
 
+/* Decode without caller-provided scratch.  (No counterpart in the reference, whose binding
+ * allocates its scratch with torch on every call.)
+ *
+ * For hosts that cannot give this library device memory at call time -- a process that forbids
+ * cudaMalloc once it is serving, a plugin slot with no allocator handle, a caller already inside
+ * code where the CUDA allocator must not be entered.  Same contract as mxdsa_decode_fwd, except
+ * that p->workspace / p->workspace_bytes are ignored: the split partials live in an array that is
+ * part of the library image, MXDSA_STATIC_SCRATCH_BYTES per GPU that loads the library, held
+ * until the process exits.  The entry point calls no cudaMalloc, cudaFree or allocating routine.
+ *
+ *  - Returns MXDSA_ERR_WORKSPACE when mxdsa_decode_workspace_bytes(b, s_q, num_sm_parts) exceeds
+ *    MXDSA_STATIC_SCRATCH_BYTES (the limit is (b + num_sm_parts) * s_q <= 255 partial slots).
+ *  - The first call on a device looks the array's device address up; make that call before any
+ *    CUDA stream capture begins on that device.
+ *  - All calls on a device share the one array and it keeps the previous call's contents.  Nothing
+ *    in it has to start at zero (every slot that is read is written earlier in the same call), but
+ *    two calls that overlap on the GPU -- different streams, or a capture replayed while another
+ *    call is in flight -- would overwrite each other's partials: serialise them. */
+#define MXDSA_STATIC_SCRATCH_BYTES (32u << 20)
+int mxdsa_decode_fwd_static(const mxdsa_decode_params* p);
+
 #ifdef __cplusplus
 }
 #endif

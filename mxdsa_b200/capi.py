@@ -14,7 +14,9 @@ LIB_PATH = os.path.join(_HERE, "lib", "libmxdsa.so")
 EXPORTS = (
     "mxdsa_status_string", "mxdsa_last_cuda_error", "mxdsa_device_fault", "mxdsa_prefill_fwd",
     "mxdsa_num_sm_parts", "mxdsa_decode_sched", "mxdsa_decode_workspace_bytes", "mxdsa_decode_fwd",
+    "mxdsa_decode_fwd_static",
 )
+STATIC_SCRATCH_BYTES = 32 << 20
 
 
 class PrefillParams(C.Structure):
@@ -75,6 +77,7 @@ def lib() -> C.CDLL:
         L.mxdsa_decode_workspace_bytes.restype = C.c_size_t
         L.mxdsa_decode_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
         L.mxdsa_decode_fwd.argtypes = [C.POINTER(DecodeParams)]
+        L.mxdsa_decode_fwd_static.argtypes = [C.POINTER(DecodeParams)]
         _lib = L
     return _lib
 

@@ -461,4 +461,49 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
     return MXDSA_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Decode for callers that cannot allocate device memory.
+//
+// Some hosts of this library hand out no allocator at all: a serving process that gives every
+// plugin a fixed memory budget and forbids cudaMalloc after start-up, or a caller that is already
+// inside a region where the CUDA allocator must not be entered.  mxdsa_decode_fwd needs scratch
+// for the split partials, and normally the caller provides it.  This variant keeps that scratch in
+// the library image instead: a file-scope device array of MXDSA_STATIC_SCRATCH_BYTES, which every
+// GPU that loads the library holds until the process exits.
+//
+// The array's name is only a host-side handle here; the device address is looked up once per
+// device with cudaGetSymbolAddress (with that device current) and then passed to the kernels like
+// any other workspace pointer.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[MXDSA_STATIC_SCRATCH_BYTES];
+
+namespace {
+void* g_static_scratch_addr[64] = {};
+std::mutex g_static_scratch_mutex;
+}  // namespace
+
+int mxdsa_decode_fwd_static(const mxdsa_decode_params* p) {
+    if (p == nullptr) return MXDSA_ERR_NULL;
+    const size_t need = mxdsa_decode_workspace_bytes(p->b, p->s_q, p->num_sm_parts);
+    if (need == 0) return MXDSA_ERR_SHAPE;
+    if (need > (size_t)MXDSA_STATIC_SCRATCH_BYTES) return MXDSA_ERR_WORKSPACE;
+    int dev = 0;
+    MX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return MXDSA_ERR_DEVICE;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (g_static_scratch_addr[dev] == nullptr) {
+            void* addr = nullptr;
+            MX_CUDA(cudaGetSymbolAddress(&addr, g_static_scratch));   // first call on this device
+            g_static_scratch_addr[dev] = addr;
+        }
+        scratch = g_static_scratch_addr[dev];
+    }
+    mxdsa_decode_params q = *p;
+    q.workspace = scratch;
+    q.workspace_bytes = MXDSA_STATIC_SCRATCH_BYTES;
+    return mxdsa_decode_fwd(&q);
+}
+
 }  // extern "C"

@@ -1,0 +1,85 @@
+"""mxdsa_decode_fwd_static: decode for callers that cannot allocate device memory.
+
+Collected last on purpose (file name), so that a failure here cannot hide the other tests.  The
+entry point keeps the split-KV partials in an array inside the library image instead of taking a
+workspace from the caller; it must give bit-identical results to mxdsa_decode_fwd, also on a second
+call that finds the previous call's partials still in the array."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _decode_params(capi, c, dev_tensors, out, lse, meta, splits, parts, workspace):
+    q, kv, idx, ekv, eidx = dev_tensors
+    w1 = (C.c_uint32 * 8)(*c["w1"])
+    w2 = (C.c_uint32 * 8)(*c["w2"])
+    have_extra = ekv is not None
+    return capi.DecodeParams(
+        b=q.shape[0], s_q=q.shape[1], topk=idx.shape[2], extra_topk=eidx.shape[2] if have_extra else 0,
+        sm_scale=c["sm_scale"], q=q.data_ptr(), stride_q_b=q.stride(0), stride_q_s=q.stride(1),
+        kv=kv.data_ptr(), num_blocks=kv.shape[0], page_block_size=kv.shape[1], stride_kv_block=kv.stride(0),
+        indices=idx.data_ptr(), stride_indices_b=idx.stride(0), stride_indices_s=idx.stride(1),
+        topk_length=None, attn_sink=None,
+        extra_kv=ekv.data_ptr() if have_extra else None, extra_num_blocks=ekv.shape[0] if have_extra else 0,
+        extra_page_block_size=ekv.shape[1] if have_extra else 0,
+        stride_extra_kv_block=ekv.stride(0) if have_extra else 0,
+        extra_indices=eidx.data_ptr() if have_extra else None,
+        stride_extra_indices_b=eidx.stride(0) if have_extra else 0,
+        stride_extra_indices_s=eidx.stride(1) if have_extra else 0, extra_topk_length=None, w1=w1, w2=w2,
+        out=out.data_ptr(), lse=lse.data_ptr(), sched_meta=meta.data_ptr(), num_splits=splits.data_ptr(),
+        num_sm_parts=parts, workspace=workspace.data_ptr() if workspace is not None else None,
+        workspace_bytes=workspace.numel() if workspace is not None else 0,
+        stream=torch.cuda.current_stream().cuda_stream)
+
+
+@pytest.mark.parametrize("name", ["decode_main_only", "decode_mtp"])
+def test_static_scratch_decode_matches_caller_scratch_decode(name):
+    from mxdsa_b200 import capi
+    L = capi.lib()
+    c = cases.build(name)
+    t = lambda x: None if x is None else torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    q, kv, idx, ekv, eidx = t(c["q"]), t(c["kv"]), t(c["indices"]), t(c["extra_kv"]), t(c["extra_indices"])
+    b, s_q = q.shape[:2]
+    parts = L.mxdsa_num_sm_parts(torch.cuda.current_device(), s_q)
+    need = L.mxdsa_decode_workspace_bytes(b, s_q, parts)
+    assert 0 < need <= capi.STATIC_SCRATCH_BYTES, "case must fit the built-in scratch"
+    meta = torch.empty((parts, 8), dtype=torch.int32, device="cuda")
+    splits = torch.empty((b + 1,), dtype=torch.int32, device="cuda")
+    sp = capi.SchedParams(b=b, s_q=s_q, topk=idx.shape[2], extra_topk=eidx.shape[2] if eidx is not None else 0,
+                          topk_length=None, extra_topk_length=None, num_sm_parts=parts,
+                          sched_meta=meta.data_ptr(), num_splits=splits.data_ptr(),
+                          stream=torch.cuda.current_stream().cuda_stream)
+    capi.check(L.mxdsa_decode_sched(C.byref(sp)), "sched")
+
+    def run(static):
+        out = torch.full((b, s_q, 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+        lse = torch.full((b, s_q, 64), float("nan"), dtype=torch.float32, device="cuda")
+        ws = None if static else torch.empty(need, dtype=torch.uint8, device="cuda")
+        p = _decode_params(capi, c, (q, kv, idx, ekv, eidx), out, lse, meta, splits, parts, ws)
+        fn = L.mxdsa_decode_fwd_static if static else L.mxdsa_decode_fwd
+        capi.check(fn(C.byref(p)), "decode")
+        capi.check(L.mxdsa_device_fault(torch.cuda.current_stream().cuda_stream), "fault")
+        return out, lse
+
+    ref_out, ref_lse = run(static=False)
+    assert not torch.isnan(ref_out.float()).any()
+    for _ in range(2):      # the second call finds the first call's partials in the array
+        out, lse = run(static=True)
+        assert torch.equal(out.view(torch.int16), ref_out.view(torch.int16))
+        assert torch.equal(lse, ref_lse)
+
+
+def test_static_scratch_decode_rejects_oversized_problems():
+    from mxdsa_b200 import capi
+    L = capi.lib()
+    # (b + parts) * s_q partial slots of 64*513*4 bytes: far beyond the built-in array
+    p = capi.DecodeParams(b=128, s_q=6, topk=128, num_sm_parts=24)
+    assert L.mxdsa_decode_workspace_bytes(128, 6, 24) > capi.STATIC_SCRATCH_BYTES
+    assert L.mxdsa_decode_fwd_static(C.byref(p)) == 6      # MXDSA_ERR_WORKSPACE
+    assert L.mxdsa_decode_fwd_static(None) == 1            # MXDSA_ERR_NULL
