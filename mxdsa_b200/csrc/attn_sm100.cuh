@@ -11,20 +11,19 @@
 //   accumulators live in tensor memory: per CTA 128 lanes x (256 O + 2 x 64 P) columns; lane L
 //   holds row L%64, and column half L/64 (P: keys 64*(L/64).., O: dims 256*(L/64)..).
 //
-// Roles (warp-specialised, 16 warps per CTA, 128 registers per thread)
-//   warps 0-1   K producers: read key indices and copy the selected rows of this CTA's 64 keys
-//               into a 3-deep K ring with 16-byte cp.async; one warp instruction moves one
+// Roles (warp-specialised, 20 warps per CTA, 96 registers per thread)
+//   warps 0-3   K producers: read key indices and copy the selected rows of this CTA's 64 keys
+//               into a 2-deep K ring with 16-byte cp.async; one warp instruction moves one
 //               512-byte row straight into the 128-byte-swizzled operand layout.  Measured on a
-//               B200 this path sustains ~40 B/clk/SM of random 512-byte rows from L2, against
-//               ~21 B/clk/SM for TMA gather4 issued from the same SM.
-//   warps 2-3   V producers: same for the 256-byte halves of all 128 keys (2-deep V ring)
-//   warp 4      CTA 0: QK issuer for even tiles      CTA 1: relays "K rows landed" to CTA 0
-//   warp 5      CTA 0: QK issuer for odd tiles       (a tcgen05.mma costs one thread ~60 cycles
-//               of issue time, so two threads alternate tiles, each with its own P buffer)
-//   warp 6      CTA 0: PV issuer                     CTA 1: relays "V rows landed" to CTA 0
-//   warp 7      operand stager: Q tile TMA + Q scale rows (per pair); K scale rows, key token
+//               B200 this path sustains ~40 B/clk/SM of random 512-byte rows from L2 with eight
+//               issuing warps (about 9 B/clk per warp), against ~21 B/clk/SM for TMA gather4.
+//   warps 4-7   V producers: same for the 256-byte halves of all 128 keys (3-deep V ring)
+//   warp 8      CTA 0: QK issuer for even tiles      CTA 1: relays "K rows landed" to CTA 0
+//   warp 9      CTA 0: QK issuer for odd tiles       (each with its own P buffer and scale columns)
+//   warp 10     CTA 0: PV issuer                     CTA 1: relays "V rows landed" to CTA 0
+//   warp 11     operand stager: Q tile TMA + Q scale rows (per pair); K scale rows, key token
 //               scales and validity bits (per tile)
-//   warps 8-15  softmax: two groups of four warps take alternate tiles (each thread one row and one
+//   warps 12-19 softmax: two groups of four warps take alternate tiles (each thread one row and one
 //               64-key half of its tile): P -> registers, running max with lazy rescale handed
 //               from group to group, exp2, token-scale, per-32-key UE8M0 requantisation to E4M3
 //               S, O rescale; both groups share the epilogue.
@@ -59,11 +58,11 @@ static constexpr int kHeads = 64;
 static constexpr int kDim = 512;
 static constexpr int kRowBytes = 528;
 static constexpr int kTileKeys = 128;    // keys per tensor-core tile
-static constexpr int kKStages = 3;       // K ring depth (32 KB per stage and CTA)
-static constexpr int kVStages = 2;       // V ring depth (32 KB per stage and CTA)
+static constexpr int kKStages = 2;       // K ring depth (32 KB per stage and CTA); freed as soon as QK is done
+static constexpr int kVStages = 3;       // V ring depth (32 KB per stage and CTA); held until PV is done
 static constexpr int kScStages = 4;      // scale/validity ring depth; also the depth of the
                                          // per-tile "QK done" / "PV done" barrier rings
-static constexpr int kThreads = 512;
+static constexpr int kThreads = 640;
 
 // tensor-memory columns
 static constexpr uint32_t kColO = 0;      // 256 columns
@@ -233,18 +232,31 @@ template <bool DECODE> struct WorkIter {
     }
 };
 
-// Key at position `j` (0..63) of 64-key block `blk` of a work item: is it attended, where are its
-// 512 data bytes (nullptr = no row, the operand rows are zero-filled) and its 16-byte scale slot.
+// Key at position `j` (0..63) of 64-key block `blk` of a work item, in two steps so that callers can
+// keep the index load and the loads that depend on it in flight for different tiles.
+// Step 1: the raw index (-1 when the position does not exist).
 template <bool DECODE>
-__device__ __forceinline__ const uint8_t* key_lookup(const AttnParams& p, const WorkItem& w, int blk, int j,
-                                                     bool& valid, const uint8_t*& slot) {
+__device__ __forceinline__ int key_index(const AttnParams& p, const WorkItem& w, int blk, int j) {
+    if (blk >= w.blk_end) return -1;
+    if constexpr (!DECODE) {
+        const int pos = blk * 64 + j;
+        return pos < p.topk ? __ldg(w.row + pos) : -1;
+    } else {
+        const bool extra = blk >= w.n_main_blocks;
+        const int pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
+        return pos < (extra ? p.extra_topk : p.topk) ? __ldg((extra ? w.erow : w.row) + pos) : -1;
+    }
+}
+// Step 2: is the key attended, where are its 512 data bytes (nullptr = no row, the operand rows are
+// zero-filled) and its 16-byte scale slot.
+template <bool DECODE>
+__device__ __forceinline__ const uint8_t* key_resolve(const AttnParams& p, const WorkItem& w, int blk, int j, int idx,
+                                                      bool& valid, const uint8_t*& slot) {
     valid = false;
     slot = nullptr;
     if (blk >= w.blk_end) return nullptr;
     if constexpr (!DECODE) {
         const int pos = blk * 64 + j;
-        if (pos >= p.topk) return nullptr;
-        const int idx = __ldg(w.row + pos);
         if (idx < 0 || idx >= p.s_kv) return nullptr;
         valid = pos < w.len;
         slot = p.kv_scales + (long long)idx * 16;
@@ -252,8 +264,6 @@ __device__ __forceinline__ const uint8_t* key_lookup(const AttnParams& p, const 
     } else {
         const bool extra = blk >= w.n_main_blocks;
         const int pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
-        const int row_len = extra ? p.extra_topk : p.topk;
-        const int idx = pos < row_len ? __ldg((extra ? w.erow : w.row) + pos) : -1;
         valid = idx != -1 && pos < (extra ? w.elen : w.len);
         if (!valid) return nullptr;
         const unsigned psz = extra ? p.extra_page_size : p.page_size;
@@ -262,6 +272,11 @@ __device__ __forceinline__ const uint8_t* key_lookup(const AttnParams& p, const 
         slot = pg + (long long)psz * kDim + (long long)in_page * 16;
         return pg + (long long)in_page * kDim;
     }
+}
+template <bool DECODE>
+__device__ __forceinline__ const uint8_t* key_lookup(const AttnParams& p, const WorkItem& w, int blk, int j,
+                                                     bool& valid, const uint8_t*& slot) {
+    return key_resolve<DECODE>(p, w, blk, j, key_index<DECODE>(p, w, blk, j), valid, slot);
 }
 
 // packed fp32 pairs (one instruction for two lanes of data)
@@ -290,6 +305,9 @@ __device__ __forceinline__ float2 f2_add(float2 a, float2 b) {
 
 // 16-byte asynchronous copy global -> shared; `bytes` = 16 copies, 0 writes zeros.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
+#ifdef MXDSA_EXP_NOCOPY
+    return;
+#endif
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 // one arrival on `bar` once all cp.async issued so far by this thread have landed
@@ -303,10 +321,10 @@ template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-// multiply 128 O columns of this thread's tensor-memory lane, starting at lane_addr, by f
-__device__ __forceinline__ void rescale_o(uint32_t lane_addr, float f) {
+// multiply the 256 O columns of this thread's tensor-memory lane by f (out of line: one copy)
+__device__ __noinline__ void rescale_o(uint32_t lane_addr, float f) {
 #pragma unroll 1
-    for (int c = 0; c < 128; c += 32) {
+    for (int c = 0; c < 256; c += 32) {
         uint32_t v[32];
         tmem_ld32(lane_addr + kColO + c, v);
         tmem_wait_ld();
@@ -315,6 +333,11 @@ __device__ __forceinline__ void rescale_o(uint32_t lane_addr, float f) {
         tmem_st32(lane_addr + kColO + c, v);
     }
     tmem_wait_st();
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 #ifdef MXDSA_PROFILE
@@ -331,26 +354,30 @@ __device__ __forceinline__ void rescale_o(uint32_t lane_addr, float f) {
 #define MXDSA_EV(gtile, id)
 #endif
 
-// latency-critical variant (issuers, softmax): polls instead of suspending
-#define MXDSA_WAIT_POLL(bar, parity, code)                                   \
-    do {                                                                     \
-        MXDSA_PROF_BEGIN                                                     \
-        if (!mbar_wait_poll(smem_u32(&(bar)), (parity), &sm.abort_word)) {   \
-            raise_fault(p, sm, (code));                                      \
-            goto done;                                                       \
-        }                                                                    \
-        MXDSA_PROF_END(code)                                                 \
+// Bounded waits, called by whole warps unless stated otherwise.  Every lane watches the barrier
+// itself: electing one lane and broadcasting the outcome was measured 50% slower end to end.
+//   MXDSA_WAIT       suspending wait (producers, stager)
+//   MXDSA_WAIT_POLL  polling with a short back-off (softmax)
+//   MXDSA_WAIT_TIGHT polling without back-off (MMA issuers)
+//   MXDSA_WAIT_THREAD  suspending wait for a role that runs as a single thread (relays)
+#ifndef MXDSA_POLL_BACKOFF_NS
+#define MXDSA_POLL_BACKOFF_NS 40
+#endif
+#define MXDSA_WAIT_ADDR_(mode, addr, parity, code)                                        \
+    do {                                                                                  \
+        MXDSA_PROF_BEGIN                                                                  \
+        if (!mbar_try_wait((addr), (parity))) {                                           \
+            if (!mbar_wait_slow((addr), (parity), &sm.abort_word, (mode))) {              \
+                raise_fault(p, sm, (code));                                               \
+                goto done;                                                                \
+            }                                                                             \
+        }                                                                                 \
+        MXDSA_PROF_END(code)                                                              \
     } while (0)
-
-#define MXDSA_WAIT(bar, parity, code)                                   \
-    do {                                                                \
-        MXDSA_PROF_BEGIN                                                \
-        if (!mbar_wait(smem_u32(&(bar)), (parity), &sm.abort_word)) {   \
-            raise_fault(p, sm, (code));                                 \
-            goto done;                                                  \
-        }                                                               \
-        MXDSA_PROF_END(code)                                            \
-    } while (0)
+#define MXDSA_WAIT_POLL(bar, parity, code) MXDSA_WAIT_ADDR_(MXDSA_POLL_BACKOFF_NS, smem_u32(&(bar)), parity, code)
+#define MXDSA_WAIT_TIGHT(bar, parity, code) MXDSA_WAIT_ADDR_(0, smem_u32(&(bar)), parity, code)
+#define MXDSA_WAIT(bar, parity, code) MXDSA_WAIT_ADDR_(-1, smem_u32(&(bar)), parity, code)
+#define MXDSA_WAIT_THREAD(bar, parity, code) MXDSA_WAIT_ADDR_(-1, smem_u32(&(bar)), parity, code)
 
 __device__ __noinline__ void raise_fault(const AttnParams& p, SmemPlan& sm, int code) {
     sm.abort_word = 1;
@@ -375,11 +402,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         mbar_init(smem_u32(&sm.bar_q_full), 2);
         mbar_init(smem_u32(&sm.bar_q_empty), 2);
         for (int i = 0; i < kKStages; ++i) {
-            mbar_init(smem_u32(&sm.bar_k_landed[i]), 64);
+            mbar_init(smem_u32(&sm.bar_k_landed[i]), 128);
             mbar_init(smem_u32(&sm.bar_k_full[i]), 1);
         }
         for (int i = 0; i < kVStages; ++i) {
-            mbar_init(smem_u32(&sm.bar_v_landed[i]), 64);
+            mbar_init(smem_u32(&sm.bar_v_landed[i]), 128);
             mbar_init(smem_u32(&sm.bar_v_full[i]), 1);
         }
         for (int i = 0; i < kScStages; ++i) {
@@ -407,7 +434,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #ifdef MXDSA_PROFILE
     const long long prof_kernel_t0 = clock64();
 #endif
-    if (warp == 7) {
+    if (warp == 11) {
         // V dimension scales: rows 0-31 feed lane quadrants 0,1 (dims of CTA 0 = w1), rows 32-63
         // quadrants 2,3 (dims of CTA 1 = w2); every row of a group is the same four words.
         for (int i = lane; i < 64; i += 32) {
@@ -422,7 +449,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     }
     __syncthreads();
     cluster_sync();
-    if (warp == 6) {
+    if (warp == 10) {
         tmem_alloc<2>(smem_u32(&sm.tmem_base), kTmemCols);
         tmem_relinquish<2>();
     }
@@ -437,215 +464,207 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     const uint64_t desc_sf = smem_desc_base(0, 128, 0);       // scale rows, 16 bytes each
 
     // ------------------------------------------------------------------ roles
-    if (warp < 2) {
-        // ===================== K producers (warps 0-1) =====================
-        // keys 64*cta + 32*warp + i (i < 32) of the tile, whole 512-byte rows, one per instruction;
-        // lane L writes byte chunk L of the row -> chunk tile L/8, 16-byte column (L%8) ^ (row%8).
+    if (warp < 8) {
+        // ===================== K producers (warps 0-3) and V producers (warps 4-7) =====================
+        // One instruction stream for both (the instruction cache is the scarce resource here); what
+        // differs is data.  K producer pw: keys 64*cta + 16*pw + i (i < 16) of the tile, whole 512-byte
+        // rows, one row per instruction; lane L writes byte chunk L of the row -> chunk tile L/8,
+        // 16-byte column (L%8) ^ (row%8).  V producer pw: keys 32*pw + 2i, 2i+1, bytes 256*cta..+255,
+        // two rows per instruction; lane L writes chunk tile (L%16)/8 of key 2i + L/16.
+        const bool isv = warp >= 4;
+        const int pw = warp & 3;
+        const int key = isv ? 32 * pw + lane : 64 * (int)cta + 16 * pw + (lane & 15);   // address this lane looks up
+        const int sel_mul = isv ? 2 : 1, sel_add = isv ? lane / 16 : 0;                 // source lane of iteration i
+        const int row0 = isv ? 32 * pw + lane / 16 : 16 * pw;                           // tile row of iteration 0
+        const uint32_t src_off = isv ? 256u * cta + (lane & 15) * 16 : lane * 16;
+        const uint32_t stage0 = isv ? smem_u32(sm.v[0]) + ((lane & 15) / 8) * 16384 : smem_u32(sm.k[0]) + (lane / 8) * 8192;
+        const uint32_t landed0 = isv ? smem_u32(&sm.bar_v_landed[0]) : smem_u32(&sm.bar_k_landed[0]);
+        const uint32_t done0 = isv ? smem_u32(&sm.bar_pv_done[0]) : smem_u32(&sm.bar_qk_done[0]);
+        const uint32_t nstages = isv ? kVStages : kKStages;
         WorkIter<DECODE> it(p);
         WorkItem w;
         uint32_t gt = 0;  // tiles issued so far
+        uint32_t s = 0;   // gt % nstages
+#pragma unroll 1
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-            const int key = 64 * (int)cta + 32 * warp + lane;
             bool valid;
             const uint8_t* slot;
             const uint8_t* ptr = key_lookup<DECODE>(p, w, w.blk_begin + key / 64, key % 64, valid, slot);
+#pragma unroll 1
             for (int t = 0; t < ntiles; ++t, ++gt) {
-                const uint32_t s = gt % kKStages;
                 const uint8_t* ptr_next = nullptr;
                 if (t + 1 < ntiles)   // prefetch the next tile's row addresses
                     ptr_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + key / 64, key % 64, valid, slot);
-                if (gt >= kKStages) {   // stage s was last used by tile gt-3
-                    const uint32_t g = gt - kKStages;
-                    MXDSA_WAIT(sm.bar_qk_done[g % kScStages], (g / kScStages) & 1, 10);
+                if (gt >= nstages) {   // stage s was last used by tile gt - nstages: its MMAs must be done
+                    const uint32_t g = gt - nstages;
+                    MXDSA_WAIT_ADDR_(-1, done0 + (g % kScStages) * 8, (g / kScStages) & 1, 10);
                 }
-                if (warp == 0 && lane == 0) { MXDSA_EV(gt, 0) }
-                const uint32_t kbase = smem_u32(sm.k[s]) + (lane / 8) * 8192;
-#pragma unroll 8
-                for (int i = 0; i < 32; ++i) {
+                if ((warp & 3) == 0 && lane == 0) { MXDSA_EV(gt, isv ? 2 : 0) }
+                const uint32_t base = stage0 + s * 32768;
+#pragma unroll 2
+                for (int i = 0; i < 16; ++i) {
                     const uint8_t* src = reinterpret_cast<const uint8_t*>(
-                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), i));
-                    const int r = 32 * warp + i;
-                    cp_async16(kbase + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + lane * 16 : p.kv,
-                               src ? 16u : 0u);
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), sel_mul * i + sel_add));
+                    const int r = row0 + sel_mul * i;
+                    cp_async16(base + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + src_off : p.kv, src ? 16u : 0u);
                 }
-                cp_async_arrive(smem_u32(&sm.bar_k_landed[s]));
-                if (warp == 0 && lane == 0) { MXDSA_EV(gt, 1) }
+                cp_async_arrive(landed0 + s * 8);
+                if ((warp & 3) == 0 && lane == 0) { MXDSA_EV(gt, isv ? 3 : 1) }
                 ptr = ptr_next;
+                s = s + 1 == nstages ? 0 : s + 1;
             }
         }
-    } else if (warp < 4) {
-        // ===================== V producers (warps 2-3) =====================
-        // keys 64*pw + j (j < 64), bytes 256*cta .. +255, two keys per instruction;
-        // lane L writes chunk tile (L%16)/8 of key 2i + L/16.
-        const int pw = warp - 2;
-        WorkIter<DECODE> it(p);
-        WorkItem w;
-        uint32_t gt = 0;
-        while (it.template next<NT>(w)) {
-            const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
-            if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-            bool valid;
-            const uint8_t* slot;
-            // block pw of the tile: lane L looks up keys L and 32+L of that block
-            const uint8_t* pa = key_lookup<DECODE>(p, w, w.blk_begin + pw, lane, valid, slot);
-            const uint8_t* pb = key_lookup<DECODE>(p, w, w.blk_begin + pw, 32 + lane, valid, slot);
-            for (int t = 0; t < ntiles; ++t, ++gt) {
-                const uint32_t s = gt % kVStages;
-                const uint8_t *pa_next = nullptr, *pb_next = nullptr;
-                if (t + 1 < ntiles) {
-                    pa_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + pw, lane, valid, slot);
-                    pb_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + pw, 32 + lane, valid, slot);
-                }
-                if (gt >= kVStages) {   // stage s was last used by tile gt-2
-                    const uint32_t g = gt - kVStages;
-                    MXDSA_WAIT(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 11);
-                }
-                if (pw == 0 && lane == 0) { MXDSA_EV(gt, 2) }
-                const uint32_t vbase = smem_u32(sm.v[s]) + ((lane & 15) / 8) * 16384;
-#pragma unroll 8
-                for (int i = 0; i < 32; ++i) {
-                    const unsigned long long pp = reinterpret_cast<unsigned long long>(i < 16 ? pa : pb);
-                    const uint8_t* src =
-                        reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, pp, (2 * i + lane / 16) & 31));
-                    const int r = 64 * pw + 2 * i + lane / 16;
-                    cp_async16(vbase + r * 128 + (((lane & 7) ^ (r & 7)) << 4),
-                               src ? src + 256 * cta + (lane & 15) * 16 : p.kv, src ? 16u : 0u);
-                }
-                cp_async_arrive(smem_u32(&sm.bar_v_landed[s]));
-                if (pw == 0 && lane == 0) { MXDSA_EV(gt, 3) }
-                pa = pa_next;
-                pb = pb_next;
-            }
-        }
-    } else if (warp == 4 || warp == 5) {
-        if (cta == 0 && lane == 0) {
+    } else if (warp == 8 || warp == 9) {
+        if (cta == 0) {
             // ===================== QK issuers (CTA 0): warp 8 even tiles, warp 9 odd tiles ==========
-            const uint32_t e = warp - 4;   // tile parity = P buffer = scale column set owned by this issuer
+            // The whole warp walks the schedule and waits; one elected lane issues.  Keeping the warp
+            // converged lets the descriptor arithmetic run on the uniform datapath, and the 16 steps
+            // are unrolled so that every operand is "base + constant": issued this way the tensor
+            // core, not the issuing thread, sets the pace (measured: 1040 cycles for a tile's 24
+            // instructions against 2670 from a single thread in a rolled loop).
+            const uint32_t e = __shfl_sync(0xffffffffu, warp - 8, 0);   // tile parity = P buffer = scale column set
             WorkIter<DECODE> it(p);
             WorkItem w;
             uint32_t gt = 0, gw = 0;
             const uint32_t qk_done_peer = map_to_cta(smem_u32(&sm.bar_qk_done[0]), 1);
             const uint32_t q_empty_peer = map_to_cta(smem_u32(&sm.bar_q_empty), 1);
             const uint64_t a_base = smem_desc(desc_k128, smem_u32(sm.q));
+            const uint32_t d_p = tmem + kColP + e * 64, sfa0 = tmem + kColQs + 4 * e, sfb0 = tmem + kColKs + 4 * e;
+#pragma unroll 1
             while (it.template next<NT>(w)) {
                 const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
                 if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
                 // Both issuers observe every phase of q_full, also for a pair in which they own no
                 // tile: a parity wait that skipped a phase would be satisfied by the stale one.
-                MXDSA_WAIT_POLL(sm.bar_q_full, gw & 1, 20);
+                MXDSA_WAIT_TIGHT(sm.bar_q_full, gw & 1, 20);
                 bool mine = false;
+#pragma unroll 1
                 for (int t = 0; t < ntiles; ++t, ++gt) {
                     if ((gt & 1) != e) continue;
                     const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
                     const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                     const uint32_t bph = (gt >> 1) & 1;
-                    if (!mine) {   // first own tile of this pair: the pair's Q scale rows
-                        tc_fence_after();
-                        tmem_cp_sf_pair(tmem + kColQs + 4 * e, smem_desc(desc_sf, smem_u32(sm.q_sf)));
-                        mine = true;
-                    }
-                    MXDSA_WAIT_POLL(sm.bar_sc_full[sc], sph, 21);
-                    MXDSA_WAIT_POLL(sm.bar_p_empty[e], bph ^ 1, 22);
-                    MXDSA_WAIT_POLL(sm.bar_k_landed[s], ph, 23);
-                    MXDSA_WAIT_POLL(sm.bar_k_full[s], ph, 24);
+                    MXDSA_WAIT_TIGHT(sm.bar_sc_full[sc], sph, 21);
+                    MXDSA_WAIT_TIGHT(sm.bar_p_empty[e], bph ^ 1, 22);
+                    MXDSA_WAIT_TIGHT(sm.bar_k_landed[s], ph, 23);
+                    MXDSA_WAIT_TIGHT(sm.bar_k_full[s], ph, 24);
                     fence_proxy_async_smem();   // rows written by cp.async are read by the tensor core
                     MXDSA_EV(gt, 6)
                     tc_fence_after();
-                    tmem_cp_sf_pair(tmem + kColKs + 4 * e, smem_desc(desc_sf, smem_u32(sm.k_sf[sc])));
-                    const uint64_t b_base = smem_desc(desc_k128, smem_u32(sm.k[s]));
+                    __syncwarp();
+                    if (elect_one()) {
+                        if (!mine)   // first own tile of this pair: the pair's Q scale rows
+                            tmem_cp_sf_pair(sfa0, smem_desc(desc_sf, smem_u32(sm.q_sf)));
+                        tmem_cp_sf_pair(sfb0, smem_desc(desc_sf, smem_u32(sm.k_sf[sc])));
+                        const uint64_t b_base = smem_desc(desc_k128, smem_u32(sm.k[s]));
 #pragma unroll
-                    for (int kk = 0; kk < 16; ++kk) {
-                        // Q bytes (kk%8)*64 + (kk/8)*32 of the row meet K bytes 32*kk
-                        const uint32_t a_off = ((kk % 8) / 2) * 8192 + ((kk % 8) % 2) * 64 + (kk / 8) * 32;
-                        const uint32_t b_off = (kk / 4) * 8192 + (kk % 4) * 32;
-                        mma_mxf8<2>(tmem + kColP + e * 64, a_base + (a_off >> 4), b_base + (b_off >> 4),
-                                    mx_idesc(128, 128, false, kk & 3, (kk / 2) & 3),
-                                    tmem + kColQs + 4 * e + 2 * ((kk / 4) & 1), tmem + kColKs + 4 * e + 2 * (kk / 8),
-                                    kk != 0);
+                        for (int kk = 0; kk < 16; ++kk) {
+                            // Q bytes (kk%8)*64 + (kk/8)*32 of the row meet K bytes 32*kk
+                            const uint32_t a_off = ((kk & 7) >> 1) * 8192 + (kk & 1) * 64 + (kk >> 3) * 32;
+                            const uint32_t b_off = (kk >> 2) * 8192 + (kk & 3) * 32;
+                            mma_mxf8<2>(d_p, a_base + (a_off >> 4), b_base + (b_off >> 4),
+                                        mx_idesc(128, 128, false, kk & 3, (kk >> 1) & 3), sfa0 + 2 * ((kk >> 2) & 1),
+                                        sfb0 + 2 * (kk >> 3), kk != 0);
+                        }
+                        mma_commit<2>(smem_u32(&sm.bar_qk_done[sc]));
+                        mma_commit<2>(qk_done_peer + sc * 8);
                     }
-                    mma_commit<2>(smem_u32(&sm.bar_qk_done[sc]));
-                    mma_commit<2>(qk_done_peer + sc * 8);
+                    __syncwarp();
+                    mine = true;
                     MXDSA_EV(gt, 7)
                 }
                 // Q may be overwritten once both issuers' QKs of this pair have finished
-                if (mine) {
-                    mma_commit<2>(smem_u32(&sm.bar_q_empty));
-                    mma_commit<2>(q_empty_peer);
-                } else {
-                    mbar_arrive(smem_u32(&sm.bar_q_empty));
-                    mbar_arrive_cluster(q_empty_peer);
+                if (elect_one()) {
+                    if (mine) {
+                        mma_commit<2>(smem_u32(&sm.bar_q_empty));
+                        mma_commit<2>(q_empty_peer);
+                    } else {
+                        mbar_arrive(smem_u32(&sm.bar_q_empty));
+                        mbar_arrive_cluster(q_empty_peer);
+                    }
                 }
+                __syncwarp();
                 ++gw;
             }
-        } else if (cta == 1 && warp == 4 && lane == 0) {
+        } else if (cta == 1 && warp == 8 && lane == 0) {
             // ===================== K relay (CTA 1) =====================
             WorkIter<DECODE> it(p);
             WorkItem w;
             uint32_t gt = 0;
             const uint32_t k_full0 = map_to_cta(smem_u32(&sm.bar_k_full[0]), 0);
+#pragma unroll 1
             while (it.template next<NT>(w)) {
                 const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
                 if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+#pragma unroll 1
                 for (int t = 0; t < ntiles; ++t, ++gt) {
                     const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
-                    MXDSA_WAIT(sm.bar_k_landed[s], ph, 12);
+                    MXDSA_WAIT_THREAD(sm.bar_k_landed[s], ph, 12);
                     fence_proxy_async_smem();
                     mbar_arrive_cluster(k_full0 + s * 8);
                 }
             }
         }
-    } else if (warp == 6) {
-        if (cta == 0 && lane == 0) {
-            // ===================== PV issuer (CTA 0) =====================
+    } else if (warp == 10) {
+        if (cta == 0) {
+            // ===================== PV issuer (CTA 0): converged warp, one elected lane issues ==========
             WorkIter<DECODE> it(p);
             WorkItem w;
             uint32_t gt = 0, gw = 0;
             const uint32_t pv_half_peer = map_to_cta(smem_u32(&sm.bar_pv_half[0]), 1);
             const uint32_t pv_done_peer = map_to_cta(smem_u32(&sm.bar_pv_done[0]), 1);
-            tmem_cp_sf_pair(tmem + kColVs, smem_desc(desc_sf, smem_u32(sm.v_sf[0])));
-            tmem_cp_sf_pair(tmem + kColVs + 4, smem_desc(desc_sf, smem_u32(sm.v_sf[1])));
+            if (elect_one()) {
+                tmem_cp_sf_pair(tmem + kColVs, smem_desc(desc_sf, smem_u32(sm.v_sf[0])));
+                tmem_cp_sf_pair(tmem + kColVs + 4, smem_desc(desc_sf, smem_u32(sm.v_sf[1])));
+            }
+            __syncwarp();
+#pragma unroll 1
             while (it.template next<NT>(w)) {
                 const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
                 if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-                MXDSA_WAIT_POLL(sm.bar_o_empty, (gw & 1) ^ 1, 30);
+                MXDSA_WAIT_TIGHT(sm.bar_o_empty, (gw & 1) ^ 1, 30);
                 tc_fence_after();
+#pragma unroll 1
                 for (int t = 0; t < ntiles; ++t, ++gt) {
                     const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
                     const uint32_t b = gt & 1, bph = (gt >> 1) & 1;
                     const uint32_t sc = gt % kScStages;
-                    MXDSA_WAIT_POLL(sm.bar_v_landed[s], ph, 31);
-                    MXDSA_WAIT_POLL(sm.bar_v_full[s], ph, 34);
+                    MXDSA_WAIT_TIGHT(sm.bar_v_landed[s], ph, 31);
+                    MXDSA_WAIT_TIGHT(sm.bar_v_full[s], ph, 34);
                     fence_proxy_async_smem();
                     const uint64_t a_base = smem_desc(desc_k128, smem_u32(sm.s[b]));
                     const uint64_t b_base = smem_desc(desc_v, smem_u32(sm.v[s]));
+                    const uint32_t sfa = tmem + kColSs + 4 * b;
+                    const bool fresh = t == 0;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        if (NT == 64 || h == 1) {   // 128-key tiles: one wait, after both halves are in
-                            MXDSA_WAIT_POLL(sm.bar_s_full[b][h], bph, 32 + h);
-                            MXDSA_EV(gt, 13 + h)
-                            tc_fence_after();
-                            tmem_cp_sf_pair(tmem + kColSs + 4 * b, smem_desc(desc_sf, smem_u32(sm.s_sf[b])));
-                        }
-                        if (NT == 128 && h == 0) continue;
+                        if (NT == 128 && h == 0) continue;   // 128-key tiles: one wait, after both halves are in
+                        MXDSA_WAIT_TIGHT(sm.bar_s_full[b][h], bph, 32 + h);
+                        MXDSA_EV(gt, 13 + h)
+                        tc_fence_after();
+                        __syncwarp();
+                        if (elect_one()) {
+                            tmem_cp_sf_pair(sfa, smem_desc(desc_sf, smem_u32(sm.s_sf[b])));
 #pragma unroll
-                        for (int ks = (NT == 64 ? 2 * h : 0); ks < 2 * h + 2; ++ks) {
-#pragma unroll
-                            for (int n = 0; n < 2; ++n) {
+                            for (int i = (NT == 64 ? 4 * h : 0); i < 4 * h + 4; ++i) {
+                                const int ks = i >> 1, n = i & 1;   // key step (32 keys), dim chunk (128 dims of each CTA)
                                 mma_mxf8<2>(tmem + kColO + n * 128, a_base + ((ks * 32) >> 4),
                                             b_base + ((n * 16384 + ks * 4096) >> 4),
-                                            mx_idesc(128, 256, true, ks, NT == 64 ? (ks & 1) : ks),
-                                            tmem + kColSs + 4 * b, tmem + kColVs + 4 * n, !(t == 0 && ks == 0));
+                                            mx_idesc(128, 256, true, ks, NT == 64 ? (ks & 1) : ks), sfa,
+                                            tmem + kColVs + 4 * n, !(fresh && ks == 0));
+                            }
+                            if (NT == 64 && h == 0) {
+                                mma_commit<2>(smem_u32(&sm.bar_pv_half[b]));
+                                mma_commit<2>(pv_half_peer + b * 8);
+                            } else {
+                                mma_commit<2>(smem_u32(&sm.bar_pv_done[sc]));
+                                mma_commit<2>(pv_done_peer + sc * 8);
                             }
                         }
-                        if (NT == 64 && h == 0) {
-                            mma_commit<2>(smem_u32(&sm.bar_pv_half[b]));
-                            mma_commit<2>(pv_half_peer + b * 8);
-                        }
+                        __syncwarp();
                     }
-                    mma_commit<2>(smem_u32(&sm.bar_pv_done[sc]));
-                    mma_commit<2>(pv_done_peer + sc * 8);
                     MXDSA_EV(gt, 15)
                 }
                 ++gw;
@@ -656,24 +675,27 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             WorkItem w;
             uint32_t gt = 0;
             const uint32_t v_full0 = map_to_cta(smem_u32(&sm.bar_v_full[0]), 0);
+#pragma unroll 1
             while (it.template next<NT>(w)) {
                 const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
                 if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+#pragma unroll 1
                 for (int t = 0; t < ntiles; ++t, ++gt) {
                     const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
-                    MXDSA_WAIT(sm.bar_v_landed[s], ph, 13);
+                    MXDSA_WAIT_THREAD(sm.bar_v_landed[s], ph, 13);
                     fence_proxy_async_smem();
                     mbar_arrive_cluster(v_full0 + s * 8);
                 }
             }
         }
-    } else if (warp == 7) {
+    } else if (warp == 11) {
         // ===================== operand stager =====================
         WorkIter<DECODE> it(p);
         WorkItem w;
         uint32_t gt = 0, gw = 0;
         const uint32_t q_full0 = map_to_cta(smem_u32(&sm.bar_q_full), 0);
         const uint32_t sc_full0 = map_to_cta(smem_u32(&sm.bar_sc_full[0]), 0);
+#pragma unroll 1
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
@@ -701,21 +723,50 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 fence_proxy_async_smem();
                 __syncwarp();
             }
-            MXDSA_WAIT(sm.bar_q_landed, gw & 1, 41);
-            if (lane == 0) mbar_arrive_cluster(q_full0);
-            // ---- per tile: K scale rows, key token scales, validity
+            // ---- per tile: K scale rows, key token scales, validity.  Two loads deep: while tile t is
+            // published, the scale slots of tile t+1 and the indices of tile t+2 are in flight.
+            // lane L looks after keys L, L+32 (block 0) and L+64, L+96 (block 1) of a tile.
+            int ix[4], ix_next[4];
+            uint2 sv_next[4];
+            uint32_t vb_next[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                ix[j] = key_index<DECODE>(p, w, w.blk_begin + j / 2, (j % 2) * 32 + lane);
+                ix_next[j] = ntiles > 1 ? key_index<DECODE>(p, w, w.blk_begin + 2 + j / 2, (j % 2) * 32 + lane) : -1;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                bool valid;
+                const uint8_t* slot;
+                key_resolve<DECODE>(p, w, w.blk_begin + j / 2, (j % 2) * 32 + lane, ix[j], valid, slot);
+                sv_next[j] = slot != nullptr ? __ldg(reinterpret_cast<const uint2*>(slot)) : make_uint2(0u, 0u);
+                vb_next[j] = __ballot_sync(0xffffffffu, valid);
+            }
+#pragma unroll 1
             for (int t = 0; t < ntiles; ++t, ++gt) {
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                 uint2 sv[4];
                 uint32_t vbits[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    // lane L looks after keys L, L+32 (block 0) and L+64, L+96 (block 1)
-                    bool valid;
-                    const uint8_t* slot;
-                    key_lookup<DECODE>(p, w, w.blk_begin + 2 * t + j / 2, (j % 2) * 32 + lane, valid, slot);
-                    sv[j] = slot != nullptr ? __ldg(reinterpret_cast<const uint2*>(slot)) : make_uint2(0u, 0u);
-                    vbits[j] = __ballot_sync(0xffffffffu, valid);
+                    sv[j] = sv_next[j];
+                    vbits[j] = vb_next[j];
+                    ix[j] = ix_next[j];
+                }
+                if (t + 1 < ntiles) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        bool valid;
+                        const uint8_t* slot;
+                        key_resolve<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + j / 2, (j % 2) * 32 + lane, ix[j], valid, slot);
+                        sv_next[j] = slot != nullptr ? __ldg(reinterpret_cast<const uint2*>(slot)) : make_uint2(0u, 0u);
+                        vb_next[j] = __ballot_sync(0xffffffffu, valid);
+                    }
+                }
+                if (t + 2 < ntiles) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        ix_next[j] = key_index<DECODE>(p, w, w.blk_begin + 2 * (t + 2) + j / 2, (j % 2) * 32 + lane);
                 }
                 if (gt >= kScStages) {   // the stage was last used by tile gt-4: its cp and its readers are done
                     MXDSA_WAIT(sm.bar_qk_done[sc], sph ^ 1, 42);
@@ -728,24 +779,29 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                     sm.tok_scale[sc][j * 32 + lane] = __uint_as_float((sv[j].x & 0xffu) << 23);
-                if (lane < 4) sm.valid[sc][lane] = vbits[lane];
+                if (lane < 4) sm.valid[sc][lane] = lane == 0 ? vbits[0] : lane == 1 ? vbits[1] : lane == 2 ? vbits[2] : vbits[3];
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(smem_u32(&sm.bar_tok_full[sc]));
                     mbar_arrive_cluster(sc_full0 + sc * 8);
                 }
+                MXDSA_EV(gt, 4)
+                if (t == 0) {   // the pair's Q tile: its latency hides behind the first tile's staging
+                    MXDSA_WAIT(sm.bar_q_landed, gw & 1, 41);
+                    if (lane == 0) mbar_arrive_cluster(q_full0);
+                }
             }
             ++gw;
         }
     } else {
-        // ===================== softmax + epilogue (warps 8-15) =====================
+        // ===================== softmax + epilogue (warps 12-19) =====================
         // Two groups of four warps take alternate tiles (group = tile parity = P buffer), so one
         // group's exp / quantise / store phase overlaps the other group's load / max phase.  Inside a
         // group a thread owns one row and one 64-key half of the tile (two UE8M0 scale groups of S).
         // The only serial link between consecutive tiles is the running maximum: after deciding m_t a
         // group publishes it (sm.m_pub) and the other group picks it up before deciding m_{t+1}.
-        const int grp = (warp - 8) >> 2;
+        const int grp = (warp - 12) >> 2;
         const int q4 = warp & 3;                 // lane quadrant of tensor memory
         const int L = q4 * 32 + lane;            // tensor-memory lane
         const int row = L % 64;                  // head
@@ -758,19 +814,23 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         WorkIter<DECODE> it(p);
         WorkItem w;
         uint32_t gt = 0, gw = 0;
+#pragma unroll 1
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
             float m_own = -1e30f;   // running max after this group's latest tile of the pair
             float l = 0.f, real_m = -CUDART_INF_F;
+#pragma unroll 1
             for (int t = 0; t < ntiles; ++t, ++gt) {
                 if ((int)(gt & 1) != grp) continue;
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                 const uint32_t b = grp, bph = (gt >> 1) & 1;
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 22) }
                 MXDSA_WAIT_POLL(sm.bar_tok_full[sc], sph, 50);
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 23) }
                 const uint32_t v0 = sm.valid[sc][2 * half], v1 = sm.valid[sc][2 * half + 1];
                 MXDSA_WAIT_POLL(sm.bar_qk_done[sc], sph, 51);
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 8) }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 8) }
                 tc_fence_after();
                 float x[64];
                 tmem_ld32(lane_addr + kColP + b * 64, reinterpret_cast<uint32_t*>(x));
@@ -779,7 +839,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(p_empty0 + b * 8);
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 9) }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 9) }
                 if ((v0 & v1) != 0xffffffffu) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) x[i] = (((i < 32 ? v0 : v1) >> (i & 31)) & 1u) ? x[i] : -CUDART_INF_F;
@@ -788,23 +848,22 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #pragma unroll
                 for (int i = 0; i < 8; ++i) mx8[i] = x[i];
 #pragma unroll
-                for (int i = 8; i < 64; i += 8) {
+                for (int i = 8; i < 64; i += 16) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) mx8[j] = fmaxf(mx8[j], x[i + j]);
+                    for (int j = 0; j < 8; ++j) mx8[j] = fmax3(mx8[j], x[i + j], x[i + 8 + j < 64 ? i + 8 + j : i + j]);
                 }
-                const float own_max = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                                            fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * p.scale_log2;
+                const float own_max = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * p.scale_log2;
                 float* xm = sm.xmax[grp][bph];
                 xm[L] = own_max;
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 16) }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 16) }
                 named_bar_sync(1 + grp, 128);
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 17) }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 17) }
                 const float peer_max = xm[L ^ 64];
                 // the running maximum handed over by the other group (value ignored on a pair's first
                 // tile, but every phase of that barrier is observed)
                 if (gt > 0) MXDSA_WAIT_POLL(sm.bar_m_ready[grp ^ 1], ((gt - 1) >> 1) & 1, 58);
                 const float m_prev = t == 0 ? -1e30f : sm.m_pub[grp ^ 1][row];
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 10) }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 10) }
                 const float sprev = (m_own == m_prev) ? 1.f : ex2_approx(m_own - m_prev);
                 // numerical tiles: NT = 128 -> one per tensor-core tile; NT = 64 -> key half 0 then 1
                 float m_used, scale0 = 1.f, scale1 = 1.f;
@@ -833,51 +892,76 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 sm.m_pub[grp][row] = m_own;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&sm.bar_m_ready[grp]));
-                // probabilities, key-scaled, re-quantised per 32 keys
+                // S buffer b is free once the PV of tile gt-2 has finished (long ago, as a rule)
+                if (gt >= 2) {
+                    const uint32_t g = gt - 2;
+                    MXDSA_WAIT_POLL(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 52);
+                }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 19) }
+                // probabilities, key-scaled, re-quantised per 32 keys and stored.  The two 32-key blocks
+                // run through ONE copy of the code (the second block's logits are moved down into the
+                // first block's registers): the instruction cache, not the register file, is scarce.
                 const float2 negm2 = make_float2(-m_used, -m_used);
                 const float4* tok4 = reinterpret_cast<const float4*>(&sm.tok_scale[sc][half * 64]);
+                uint8_t* srow = sm.s[b];
                 float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-                uint32_t s8[16];
                 uint32_t e_bytes = 0;
-#pragma unroll
+#pragma unroll 1
                 for (int g = 0; g < 2; ++g) {
-                    float am4[4] = {0.f, 0.f, 0.f, 0.f};
+                    uint32_t s8[8];
+#ifdef MXDSA_EXP_NOSOFTMAX
 #pragma unroll
-                    for (int i = 32 * g; i < 32 * g + 32; i += 4) {
-#ifdef MXDSA_EXP_NOTOK
-                        const float4 tk = make_float4(1.f, 1.f, 1.f, 1.f);
-                        (void)tok4;
+                    for (int i = 0; i < 8; ++i) s8[i] = 0x38383838u;
+                    uint32_t e = 0x7f;
+                    if (false)
 #else
-                        const float4 tk = tok4[i / 4];
+                    uint32_t e;
 #endif
-                        float2 a = f2_fma(make_float2(x[i], x[i + 1]), scale2, negm2);
-                        float2 c = f2_fma(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
-                        a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
-                        c = make_float2(ex2_approx(c.x), ex2_approx(c.y));
-                        sum2[0] = f2_add(sum2[0], a);
-                        sum2[1] = f2_add(sum2[1], c);
-                        a = f2_mul(a, make_float2(tk.x, tk.y));
-                        c = f2_mul(c, make_float2(tk.z, tk.w));
-                        am4[0] = fmaxf(am4[0], a.x);
-                        am4[1] = fmaxf(am4[1], a.y);
-                        am4[2] = fmaxf(am4[2], c.x);
-                        am4[3] = fmaxf(am4[3], c.y);
-                        x[i] = a.x; x[i + 1] = a.y; x[i + 2] = c.x; x[i + 3] = c.y;
-                    }
-                    const float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
-                    uint32_t e = cvt_ue8m0_roundup(amax > 0.f ? __fdividef(amax, 448.0f) : 1.0f);
-                    e = max(e, 61u);
-                    e_bytes |= e << (8 * g);
-                    const float mulf = __uint_as_float((254u - e) << 23);
-                    const float2 mul2 = make_float2(mulf, mulf);
-                    if (g == 0 && warp == 8 && lane == 0) { MXDSA_EV(gt, 18) }
+                    {
+                        float am = 0.f;
 #pragma unroll
-                    for (int i = 32 * g; i < 32 * g + 32; i += 4) {
-                        const float2 a = f2_mul(make_float2(x[i], x[i + 1]), mul2);
-                        const float2 c = f2_mul(make_float2(x[i + 2], x[i + 3]), mul2);
-                        s8[i / 4] = (uint32_t)cvt_e4m3x2(a.x, a.y) | ((uint32_t)cvt_e4m3x2(c.x, c.y) << 16);
+                        for (int i = 0; i < 32; i += 4) {
+#ifdef MXDSA_EXP_NOTOK
+                            const float4 tk = make_float4(1.f, 1.f, 1.f, 1.f);
+                            (void)tok4;
+#else
+                            const float4 tk = tok4[g * 8 + i / 4];
+#endif
+                            float2 a = f2_fma(make_float2(x[i], x[i + 1]), scale2, negm2);
+                            float2 c = f2_fma(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
+                            a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
+                            c = make_float2(ex2_approx(c.x), ex2_approx(c.y));
+                            sum2[0] = f2_add(sum2[0], a);
+                            sum2[1] = f2_add(sum2[1], c);
+                            a = f2_mul(a, make_float2(tk.x, tk.y));
+                            c = f2_mul(c, make_float2(tk.z, tk.w));
+                            am = fmax3(am, a.x, a.y);
+                            am = fmax3(am, c.x, c.y);
+                            x[i] = a.x; x[i + 1] = a.y; x[i + 2] = c.x; x[i + 3] = c.y;
+                        }
+                        e = cvt_ue8m0_roundup(am > 0.f ? __fdividef(am, 448.0f) : 1.0f);
+                        e = max(e, 61u);
+                        const float mulf = __uint_as_float((254u - e) << 23);
+                        const float2 mul2 = make_float2(mulf, mulf);
+                        if (g == 0 && warp == 12 && lane == 0) { MXDSA_EV(gt, 18) }
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const float2 a = f2_mul(make_float2(x[i], x[i + 1]), mul2);
+                            const float2 c = f2_mul(make_float2(x[i + 2], x[i + 3]), mul2);
+                            s8[i / 4] = (uint32_t)cvt_e4m3x2(a.x, a.y) | ((uint32_t)cvt_e4m3x2(c.x, c.y) << 16);
+                        }
+                    }
+                    e_bytes |= e << (8 * g);
+                    *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + g * 32)) = make_uint4(s8[0], s8[1], s8[2], s8[3]);
+                    *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + g * 32 + 16)) = make_uint4(s8[4], s8[5], s8[6], s8[7]);
+                    if (g == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) x[i] = x[32 + i];
                     }
                 }
+                // scale rows: row (row%32) and its copy at +32; word row/32; bytes 2*half, 2*half+1
+                reinterpret_cast<uint16_t*>(&sm.s_sf[b][(row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
+                reinterpret_cast<uint16_t*>(&sm.s_sf[b][(32 + row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
                 const float2 s2 = f2_add(sum2[0], sum2[1]);
                 const float sum = s2.x + s2.y;
                 // l bookkeeping: every update of m rescales all partial sums of the row
@@ -887,43 +971,25 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     if (half == 0) l = fmaf(l * sprev, scale0, sum) * scale1;
                     else l = fmaf(l * sprev * scale0, scale1, sum);
                 }
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 11) }
-                // S buffer b is free once the PV of tile gt-2 has finished
-                if (gt >= 2) {
-                    const uint32_t g = gt - 2;
-                    MXDSA_WAIT_POLL(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 52);
-                }
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 19) }
-                {
-                    uint8_t* srow = sm.s[b];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + i * 16)) =
-                            make_uint4(s8[4 * i], s8[4 * i + 1], s8[4 * i + 2], s8[4 * i + 3]);
-                    // scale rows: row (row%32) and its copy at +32; word row/32; bytes 2*half, 2*half+1
-                    reinterpret_cast<uint16_t*>(&sm.s_sf[b][(row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
-                    reinterpret_cast<uint16_t*>(&sm.s_sf[b][(32 + row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
-                }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 11) }
                 // O rescale before the first key half is accumulated (this thread: its whole lane)
                 if (grow0 && t > 0) {
                     MXDSA_WAIT_POLL(sm.bar_pv_done[(gt - 1) % kScStages], ((gt - 1) / kScStages) & 1, 53);
                     tc_fence_after();
                     rescale_o(lane_addr, scale0);
-                    rescale_o(lane_addr + 128, scale0);
                     tc_fence_before();
                 }
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 20) }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 20) }
                 fence_proxy_async_smem();
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 21) }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 21) }
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(s_full0 + (b * 2 + 0) * 8);
-                if (warp == 8 && lane == 0) { MXDSA_EV(gt, 12) }
+                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 12) }
                 if constexpr (NT == 64) {
                     if (grow1) {
                         MXDSA_WAIT_POLL(sm.bar_pv_half[b], bph, 54);
                         tc_fence_after();
                         rescale_o(lane_addr, scale1);
-                        rescale_o(lane_addr + 128, scale1);
                         tc_fence_before();
                     }
                 }
@@ -1020,8 +1086,8 @@ done:
     // After a fault, softmax threads leave at different points; one extra arrival per leaving thread
     // completes the exchange barrier for those still parked on it (they fail their next wait and
     // follow).  In a normal exit the arrivals are harmless: nobody waits on that barrier any more.
-    if (warp >= 8) {
-        named_bar_arrive(1 + ((warp - 8) >> 2), 128);
+    if (warp >= 12) {
+        named_bar_arrive(1 + ((warp - 12) >> 2), 128);
         named_bar_arrive(3, 256);
     }
     tc_fence_before();
@@ -1035,7 +1101,7 @@ done:
     }
 #endif
     cluster_sync();
-    if (warp == 6) tmem_dealloc<2>(tmem, kTmemCols);
+    if (warp == 10) tmem_dealloc<2>(tmem, kTmemCols);
 }
 
 }  // namespace mxdsa

@@ -147,12 +147,43 @@ SM100_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_w
 }
 // Polling flavour for latency-critical waiters (a handful of threads per CTA): no suspension, so the
 // waiter resumes within a few cycles of the arrival.  Same ~0.6 s bound, counted in SM cycles.
+template <int BACKOFF_NS = 0>
 SM100_DEVICE bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* abort_word) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
+        // a short sleep between polls keeps a waiting warp from taking issue slots away from the
+        // warps on the same scheduler that have work (the MMA-issuing threads above all)
+        if (BACKOFF_NS > 0) __nanosleep(BACKOFF_NS);
+        if ((++spins & 255u) == 0) {
+            if (*abort_word != 0) return false;
+            if (clock64() - t0 > 1200000000LL) {
+                *abort_word = 1;
+                return false;
+            }
+        }
+    }
+}
+// Out-of-line slow path shared by every wait site of a kernel.  A kernel with many wait sites and
+// many concurrent roles lives or dies by its instruction footprint (the SM's instruction cache
+// holds about 32 KB), so a site inlines only the first try and calls this when it fails.
+// backoff_ns < 0: suspending wait; 0: tight polling; > 0: polling with that sleep between polls.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_word, int backoff_ns) {
+    if (backoff_ns < 0) {
+        for (int i = 0; i < kWaitSlices; ++i) {
+            if (mbar_try_wait_suspend(bar, parity, kWaitSliceNs, false)) return true;
+            if (*abort_word != 0) return false;
+        }
+        *abort_word = 1;
+        return false;
+    }
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (backoff_ns > 0) __nanosleep(backoff_ns);
         if ((++spins & 255u) == 0) {
             if (*abort_word != 0) return false;
             if (clock64() - t0 > 1200000000LL) {
