@@ -166,6 +166,7 @@ struct __align__(1024) SmemPlan {
     uint64_t bar_m_ready[2];                       // local: group g published the running max of its tile
     uint32_t tmem_base;
     int abort_word;
+    DeviceFault* fault;                            // copy of the kernel parameter, for the out-of-line wait path
 #ifdef MXDSA_PROFILE
     unsigned long long prof[64];
     int ev[16][24];
@@ -363,35 +364,58 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 #ifndef MXDSA_POLL_BACKOFF_NS
 #define MXDSA_POLL_BACKOFF_NS 40
 #endif
-#define MXDSA_WAIT_ADDR_(mode, addr, parity, code)                                        \
-    do {                                                                                  \
-        MXDSA_PROF_BEGIN                                                                  \
-        if (!mbar_try_wait((addr), (parity))) {                                           \
-            if (!mbar_wait_slow((addr), (parity), &sm.abort_word, (mode))) {              \
-                raise_fault(p, sm, (code));                                               \
-                goto done;                                                                \
-            }                                                                             \
-        }                                                                                 \
-        MXDSA_PROF_END(code)                                                              \
+// The loops are written out at every site, as lean as they get (a counter, not a clock), and the
+// only call -- raise_fault -- sits on the path that never comes back, so no register has to survive
+// it: a call on the waiting path costs about 1 KB of save/restore code per site, and the kernel's
+// instruction footprint is what limits it (the SM's instruction cache holds about 32 KB).
+// Bounds: polling 2^24 tries (>= 0.2 s), suspending 6000 slices of 100 us.
+#define MXDSA_WAIT_ADDR_(mode, addr, parity, code)                                                  \
+    do {                                                                                            \
+        MXDSA_PROF_BEGIN                                                                            \
+        if (__builtin_expect(!mbar_try_wait((addr), (parity)), 0)) {                                \
+            uint32_t spins__ = 0;                                                                   \
+            while (true) {                                                                          \
+                if ((mode) < 0) {                                                                   \
+                    if (mbar_try_wait_suspend((addr), (parity), kWaitSliceNs, false)) break;        \
+                    if (++spins__ > (uint32_t)kWaitSlices || *(volatile int*)&sm.abort_word != 0) { \
+                        raise_fault(sm, (code));                                                    \
+                        goto done;                                                                  \
+                    }                                                                               \
+                } else {                                                                            \
+                    if ((mode) > 0) __nanosleep((mode) > 0 ? (mode) : 1);                           \
+                    if (mbar_try_wait((addr), (parity))) break;                                     \
+                    if ((++spins__ & 1023u) == 0 &&                                                 \
+                        (spins__ >= (1u << 24) || *(volatile int*)&sm.abort_word != 0)) {           \
+                        raise_fault(sm, (code));                                                    \
+                        goto done;                                                                  \
+                    }                                                                               \
+                }                                                                                   \
+            }                                                                                       \
+        }                                                                                           \
+        MXDSA_PROF_END(code)                                                                        \
     } while (0)
 #define MXDSA_WAIT_POLL(bar, parity, code) MXDSA_WAIT_ADDR_(MXDSA_POLL_BACKOFF_NS, smem_u32(&(bar)), parity, code)
 #define MXDSA_WAIT_TIGHT(bar, parity, code) MXDSA_WAIT_ADDR_(0, smem_u32(&(bar)), parity, code)
 #define MXDSA_WAIT(bar, parity, code) MXDSA_WAIT_ADDR_(-1, smem_u32(&(bar)), parity, code)
 #define MXDSA_WAIT_THREAD(bar, parity, code) MXDSA_WAIT_ADDR_(-1, smem_u32(&(bar)), parity, code)
 
-__device__ __noinline__ void raise_fault(const AttnParams& p, SmemPlan& sm, int code) {
+// A wait was abandoned: mark both CTAs of the pair and the device fault record.
+__device__ __noinline__ void raise_fault(SmemPlan& sm, int code) {
     sm.abort_word = 1;
     // tell the peer CTA so that its roles stop waiting as well
     const uint32_t peer = map_to_cta(smem_u32(&sm.abort_word), cluster_cta_rank() ^ 1u);
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer), "r"(1) : "memory");
-    if (atomicCAS(&p.fault->flag, 0, 1) == 0) p.fault->where = code;
+    if (atomicCAS(&sm.fault->flag, 0, 1) == 0) sm.fault->where = code;
 }
 
 template <bool DECODE, int NT>
 __global__ void __launch_bounds__(kThreads, 1)
 mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ TensorMaps maps) {
     extern __shared__ uint8_t smem_raw[];
-    SmemPlan& sm = *reinterpret_cast<SmemPlan*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // The plan starts at the first 1024-byte boundary.  The pointer is formed by adding an offset to
+    // the shared array (not by rounding an integer), so the compiler still knows that every access
+    // through it is a shared-memory access and emits 32-bit shared loads and stores.
+    SmemPlan& sm = *reinterpret_cast<SmemPlan*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
     const uint32_t cta = cluster_cta_rank();
@@ -426,6 +450,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         mbar_init(smem_u32(&sm.bar_m_ready[0]), 4);
         mbar_init(smem_u32(&sm.bar_m_ready[1]), 4);
         sm.abort_word = 0;
+        sm.fault = p.fault;
 #ifdef MXDSA_PROFILE
         for (int i = 0; i < 64; ++i) sm.prof[i] = 0;
 #endif
