@@ -50,6 +50,13 @@
 
 #include "sm100_ptx.cuh"
 
+#ifndef MXDSA_REGS_COPY
+#define MXDSA_REGS_COPY 64
+#endif
+#ifndef MXDSA_REGS_CTL
+#define MXDSA_REGS_CTL 64
+#endif
+
 namespace mxdsa {
 
 using namespace sm100;
@@ -489,7 +496,20 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     const uint64_t desc_sf = smem_desc_base(0, 128, 0);       // scale rows, 16 bytes each
 
     // ------------------------------------------------------------------ roles
+    // Register budget: the launch gives every thread 96 (640 x 96 = 61440, and that -- not the SM's
+    // whole file -- is the pool setmaxnreg draws from; an increase beyond it would block for ever).
+    // The copy and control warps hand most of theirs back so that the softmax warps (64 logits per
+    // thread in registers) can work without spilling: 8 x 32 x 56 + 4 x 32 x 64 + 8 x 32 x 152 = 61440.
+    // Each setmaxnreg is executed by the four warps of one aligned warp group with the same value.
+    // Measured: prefill gains 8%, decode (short work items, heavier address arithmetic in the copy
+    // warps) loses 15%, so only prefill rebalances.
+    constexpr bool kRebalanceRegs = !DECODE;
+    constexpr int kRegsCopy = MXDSA_REGS_COPY, kRegsCtl = MXDSA_REGS_CTL;
+    constexpr int kRegsSoftmax = (kThreads * 96 - 8 * 32 * kRegsCopy - 4 * 32 * kRegsCtl) / (8 * 32);
+    static_assert(kRegsSoftmax % 8 == 0 && 8 * 32 * kRegsCopy + 4 * 32 * kRegsCtl + 8 * 32 * kRegsSoftmax == kThreads * 96,
+                  "register budget must add up to the launch allocation exactly");
     if (warp < 8) {
+        if constexpr (kRebalanceRegs) setmaxnreg_dec<kRegsCopy>();
         // ===================== K producers (warps 0-3) and V producers (warps 4-7) =====================
         // One instruction stream for both (the instruction cache is the scarce resource here); what
         // differs is data.  K producer pw: keys 64*cta + 16*pw + i (i < 16) of the tile, whole 512-byte
@@ -514,34 +534,41 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-            bool valid;
-            const uint8_t* slot;
-            const uint8_t* ptr = key_lookup<DECODE>(p, w, w.blk_begin + key / 64, key % 64, valid, slot);
+            // iteration t looks up the row addresses of tile t+1 (one look-up site) and copies tile t
+            const uint8_t* ptr = nullptr;
 #pragma unroll 1
-            for (int t = 0; t < ntiles; ++t, ++gt) {
+            for (int t = -1; t < ntiles; ++t) {
                 const uint8_t* ptr_next = nullptr;
-                if (t + 1 < ntiles)   // prefetch the next tile's row addresses
+                if (t + 1 < ntiles) {
+                    bool valid;
+                    const uint8_t* slot;
                     ptr_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + key / 64, key % 64, valid, slot);
-                if (gt >= nstages) {   // stage s was last used by tile gt - nstages: its MMAs must be done
-                    const uint32_t g = gt - nstages;
-                    MXDSA_WAIT_ADDR_(-1, done0 + (g % kScStages) * 8, (g / kScStages) & 1, 10);
                 }
-                if ((warp & 3) == 0 && lane == 0) { MXDSA_EV(gt, isv ? 2 : 0) }
-                const uint32_t base = stage0 + s * 32768;
+                if (t >= 0) {
+                    if (gt >= nstages) {   // stage s was last used by tile gt - nstages: its MMAs must be done
+                        const uint32_t g = gt - nstages;
+                        MXDSA_WAIT_ADDR_(-1, done0 + (g % kScStages) * 8, (g / kScStages) & 1, 10);
+                    }
+                    if ((warp & 3) == 0 && lane == 0) { MXDSA_EV(gt, isv ? 2 : 0) }
+                    const uint32_t base = stage0 + s * 32768;
 #pragma unroll 2
-                for (int i = 0; i < 16; ++i) {
-                    const uint8_t* src = reinterpret_cast<const uint8_t*>(
-                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), sel_mul * i + sel_add));
-                    const int r = row0 + sel_mul * i;
-                    cp_async16(base + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + src_off : p.kv, src ? 16u : 0u);
+                    for (int i = 0; i < 16; ++i) {
+                        const uint8_t* src = reinterpret_cast<const uint8_t*>(
+                            __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), sel_mul * i + sel_add));
+                        const int r = row0 + sel_mul * i;
+                        cp_async16(base + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + src_off : p.kv, src ? 16u : 0u);
+                    }
+                    cp_async_arrive(landed0 + s * 8);
+                    if ((warp & 3) == 0 && lane == 0) { MXDSA_EV(gt, isv ? 3 : 1) }
+                    s = s + 1 == nstages ? 0 : s + 1;
+                    ++gt;
                 }
-                cp_async_arrive(landed0 + s * 8);
-                if ((warp & 3) == 0 && lane == 0) { MXDSA_EV(gt, isv ? 3 : 1) }
                 ptr = ptr_next;
-                s = s + 1 == nstages ? 0 : s + 1;
             }
         }
-    } else if (warp == 8 || warp == 9) {
+    } else if (warp < 12) {
+    if constexpr (kRebalanceRegs) setmaxnreg_dec<kRegsCtl>();
+    if (warp == 8 || warp == 9) {
         if (cta == 0) {
             // ===================== QK issuers (CTA 0): warp 8 even tiles, warp 9 odd tiles ==========
             // The whole warp walks the schedule and waits; one elected lane issues.  Keeping the warp
@@ -751,34 +778,19 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             // ---- per tile: K scale rows, key token scales, validity.  Two loads deep: while tile t is
             // published, the scale slots of tile t+1 and the indices of tile t+2 are in flight.
             // lane L looks after keys L, L+32 (block 0) and L+64, L+96 (block 1) of a tile.
-            int ix[4], ix_next[4];
-            uint2 sv_next[4];
-            uint32_t vb_next[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                ix[j] = key_index<DECODE>(p, w, w.blk_begin + j / 2, (j % 2) * 32 + lane);
-                ix_next[j] = ntiles > 1 ? key_index<DECODE>(p, w, w.blk_begin + 2 + j / 2, (j % 2) * 32 + lane) : -1;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                bool valid;
-                const uint8_t* slot;
-                key_resolve<DECODE>(p, w, w.blk_begin + j / 2, (j % 2) * 32 + lane, ix[j], valid, slot);
-                sv_next[j] = slot != nullptr ? __ldg(reinterpret_cast<const uint2*>(slot)) : make_uint2(0u, 0u);
-                vb_next[j] = __ballot_sync(0xffffffffu, valid);
-            }
+            int ix[4] = {-1, -1, -1, -1};
+            uint2 sv_next[4] = {};
+            uint32_t vb_next[4] = {};
 #pragma unroll 1
-            for (int t = 0; t < ntiles; ++t, ++gt) {
-                const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
+            for (int t = -2; t < ntiles; ++t) {
                 uint2 sv[4];
                 uint32_t vbits[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     sv[j] = sv_next[j];
                     vbits[j] = vb_next[j];
-                    ix[j] = ix_next[j];
                 }
-                if (t + 1 < ntiles) {
+                if (t + 1 >= 0 && t + 1 < ntiles) {   // scale slots of tile t+1 (its indices arrived during the last iteration)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         bool valid;
@@ -788,11 +800,13 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                         vb_next[j] = __ballot_sync(0xffffffffu, valid);
                     }
                 }
-                if (t + 2 < ntiles) {
+                if (t + 2 < ntiles) {   // indices of tile t+2
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        ix_next[j] = key_index<DECODE>(p, w, w.blk_begin + 2 * (t + 2) + j / 2, (j % 2) * 32 + lane);
+                        ix[j] = key_index<DECODE>(p, w, w.blk_begin + 2 * (t + 2) + j / 2, (j % 2) * 32 + lane);
                 }
+                if (t < 0) continue;
+                const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                 if (gt >= kScStages) {   // the stage was last used by tile gt-4: its cp and its readers are done
                     MXDSA_WAIT(sm.bar_qk_done[sc], sph ^ 1, 42);
                     MXDSA_WAIT(sm.bar_tok_empty[sc], sph ^ 1, 43);
@@ -816,10 +830,13 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     MXDSA_WAIT(sm.bar_q_landed, gw & 1, 41);
                     if (lane == 0) mbar_arrive_cluster(q_full0);
                 }
+                ++gt;
             }
             ++gw;
         }
+    }
     } else {
+        if constexpr (kRebalanceRegs) setmaxnreg_inc<kRegsSoftmax>();
         // ===================== softmax + epilogue (warps 12-19) =====================
         // Two groups of four warps take alternate tiles (group = tile parity = P buffer), so one
         // group's exp / quantise / store phase overlaps the other group's load / max phase.  Inside a
