@@ -251,6 +251,40 @@ def reference_gpu(torch, q, kv, idx, w1, w2, steps, warmup):
         return dict(unavailable=repr(ex)[:200])
 
 
+def run_profile_case(which: str):
+    """Three launches of a small case of one kernel: inputs larger than L2, well under a GB on the
+    device, each launch a millisecond or two -- the size a multi-pass profiler capture wants."""
+    import torch
+    import mxdsa_b200 as M
+    torch.cuda.set_device(0)
+    if which == "prefill":
+        s_q = 4096                                     # Q = 138 MB; same kv_len / topk as the headline
+        q, kv, idx, w1, w2 = make_prefill_inputs(torch, s_q, seed=100)
+        for _ in range(3):
+            M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, 512 ** -0.5, w1, w2, None, None)
+        case = {"kernel": "mxdsa_attn_kernel<prefill,128>", "s_q": s_q, "kv_len": S_KV, "topk": TOPK}
+    else:
+        from mxdsa_b200 import packing as P
+        b, s_q, extra = 32, 6, 4096                    # 32 requests x 8.65 MB of private extra pages = 277 MB
+        g = torch.Generator(device="cuda").manual_seed(3)
+        q = P.pack_dual_q64(torch.randn(b * s_q, HEADS, 512, device="cuda", generator=g))[0].view(b, s_q, HEADS, 528)
+        kvf, w1, w2 = P.make_rank1_kv((2 * b, 64, 1), device="cuda", generator=g)
+        kv = P.pack_dual_decode_kv_pages(kvf)[0]
+        pool = P.pack_dual_decode_kv_pages(torch.randn(256, 64, 1, 512, device="cuda", generator=g))[0]
+        ekv = pool.repeat(b, 1, 1, 1)
+        off = torch.arange(b, device="cuda", dtype=torch.int32)[:, None, None]
+        idx = (torch.rand(b * s_q, 128, device="cuda", generator=g).argsort(1).int().view(b, s_q, 128) + off * 128).contiguous()
+        eidx = (torch.rand(b * s_q, 16384, device="cuda", generator=g).argsort(1)[:, :extra].int()
+                .view(b, s_q, extra) + off * 16384).contiguous()
+        for _ in range(3):
+            M.dual_mxfp8_sparse_decode_fwd(q, kv, idx, None, None, None, None, ekv, eidx, None, 512, 512, 512 ** -0.5,
+                                           w1, w2)
+        case = {"kernel": "mxdsa_attn_kernel<decode,64> + mxdsa_combine_kernel", "b": b, "s_q": s_q, "extra_topk": extra}
+    torch.cuda.synchronize()
+    M.device_fault()
+    print(json.dumps({"profile_case": which, **case, "launches": 3}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -259,7 +293,11 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--sq", type=int, default=S_Q, help="query tokens per GPU (default: the headline 65536)")
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu baseline, decode and comparator")
+    ap.add_argument("--profile-case", choices=["prefill", "decode"], default=None,
+                    help="launch a small case of one kernel a few times and exit (for profiler captures; no timing)")
     args = ap.parse_args()
+    if args.profile_case:
+        return run_profile_case(args.profile_case)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -295,8 +333,14 @@ def main():
     kern_ms = statistics.median(per)
     achieved = prefill_flops(s_q, TOPK) / kern_ms / 1e9
     peak = 2.0 * peaks["bf16_tflops_sustained"]
+    # DRAM traffic of one launch: dram__bytes_read + dram__bytes_write of this kernel from the ncu capture
+    # of `bench.py --profile-case prefill` (s_q = 4096: 180.9 MB read of which 8.65 MB is the KV that
+    # does not grow with s_q, 218.0 MB written), scaled by the query tokens of this launch.
+    traffic = ((180.9e6 - 8.65e6) + 218.0e6) * (s_q / 4096.0) + 8.65e6
     roofline = dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
-                    traffic=None, peak_source=f"2 x {peaks['source']} sustained bf16 GEMM TFLOP/s",
+                    traffic=traffic, traffic_unit="bytes per launch (ncu small-case capture scaled by query tokens)",
+                    algorithmic_bytes=s_q * (HEADS * 528 + TOPK * 2 + HEADS * 512 * 2 + HEADS * 8) + S_KV * 528,
+                    peak_source=f"2 x {peaks['source']} sustained bf16 GEMM TFLOP/s",
                     frac_of_nominal_4500=achieved / 4500.0)
 
     result = {

@@ -350,12 +350,20 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 
 #ifdef MXDSA_PROFILE
 // per-wait stall accounting (cycles spent in each numbered wait, summed over the lanes' leader)
+#ifdef MXDSA_PROFILE_LIGHT   // event stamps only, and only those of MXDSA_EV_MASK: perturbs the timeline far less
+#define MXDSA_PROF_BEGIN
+#define MXDSA_PROF_END(code)
+#else
 #define MXDSA_PROF_BEGIN const long long prof_t0__ = clock64();
 #define MXDSA_PROF_END(code) \
     if (lane == 0) atomicAdd(&sm.prof[(code)], (unsigned long long)(clock64() - prof_t0__));
+#endif
+#ifndef MXDSA_EV_MASK
+#define MXDSA_EV_MASK 0xffffffu
+#endif
 // event trace: cycle stamps of tiles 16..31 of this CTA (profiling builds only)
 #define MXDSA_EV(gtile, id) \
-    if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
+    if ((((MXDSA_EV_MASK) >> (id)) & 1u) && (gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
 #else
 #define MXDSA_PROF_BEGIN
 #define MXDSA_PROF_END(code)
@@ -402,7 +410,10 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
         MXDSA_PROF_END(code)                                                                        \
     } while (0)
 #define MXDSA_WAIT_POLL(bar, parity, code) MXDSA_WAIT_ADDR_(MXDSA_POLL_BACKOFF_NS, smem_u32(&(bar)), parity, code)
-#define MXDSA_WAIT_TIGHT(bar, parity, code) MXDSA_WAIT_ADDR_(0, smem_u32(&(bar)), parity, code)
+#ifndef MXDSA_TIGHT_BACKOFF_NS
+#define MXDSA_TIGHT_BACKOFF_NS 0
+#endif
+#define MXDSA_WAIT_TIGHT(bar, parity, code) MXDSA_WAIT_ADDR_(MXDSA_TIGHT_BACKOFF_NS, smem_u32(&(bar)), parity, code)
 #define MXDSA_WAIT(bar, parity, code) MXDSA_WAIT_ADDR_(-1, smem_u32(&(bar)), parity, code)
 #define MXDSA_WAIT_THREAD(bar, parity, code) MXDSA_WAIT_ADDR_(-1, smem_u32(&(bar)), parity, code)
 
