@@ -7,7 +7,7 @@
 
 Workload (config.workload): the reference's headline prefill point -- 65 536 query tokens per GPU,
 64 heads, one 512-wide MXFP8 KV head, kv_len 16 384, pair-shared rows of 4096 distinct indices
-(BASELINE config 1; with N GPUs the query pairs are sharded contiguously, KV is replicated and
+(with N GPUs the query pairs are sharded contiguously, KV is replicated and
 nothing is exchanged, so N = 8 is the 524 288-token configuration).  Inputs are synthetic with
 the reference benchmark's distributions (N(0,1) values through the packers); no dataset exists
 for this path.  One "step" = one call of the prefill entry point over the rank's tokens.
@@ -17,7 +17,8 @@ Printed JSON (one line, rank 0):
              resident in HBM, CUDA-event time, max over ranks
   e2e        same metric through the public entry point with HOST buffers: pinned Q / KV / indices
              copied in and out / lse / max_logits copied back inside the timed region
-  roofline   the attention kernel against the tensor-core roof (see DESIGN.md for the peak used)
+  roofline   the attention kernel against the tensor-core roof: peak = 2 x the measured sustained dense
+             bf16 GEMM rate (MXFP8 runs at twice the bf16 rate; no MXFP8 GEMM peak is measured)
   cpu_baseline  the torch dequantise-and-gather CPU path on a bounded sample (rank 0, N = 1)
   decode     the reference's decode headline (batch 128, sq 6, main 128 + extra 4096 of 16 384):
              latency and gathered GB/s against the measured HBM roof (N = 1 only)
