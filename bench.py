@@ -234,6 +234,46 @@ def decode_headline(torch, M, peaks, steps, warmup):
                 l2_flush="256 MiB written between iterations", launches_per_step=2)
 
 
+def pack_headline(torch, peaks, steps, warmup):
+    """The step in front of the path: fused quantise-and-pack of Q (16 384 tokens x 64 heads of bf16
+    activations, 1.07 GB in, 0.55 GB out) and of a 65 536-token KV cache, against the HBM roof; the torch
+    kernel chain that the reference's helper launches for the same tensor is timed beside it."""
+    from mxdsa_b200 import packing as P, quantize as Z
+    g = torch.Generator(device="cuda").manual_seed(9)
+    out = {}
+    for name, shape, fused, chain in (
+            ("pack_q", (16384, HEADS, 512), Z.pack_dual_q64, lambda t: P.pack_dual_q64(t)[0]),
+            ("pack_kv", (65536 * 8, 1, 512), Z.pack_dual_prefill_kv64, lambda t: P.pack_dual_prefill_kv64(t)[0])):
+        x = torch.randn(shape, device="cuda", generator=g).bfloat16()
+        rows = x.numel() // 512
+        alg_bytes = rows * (512 * 2 + 528)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+        def timed(fn, n):
+            for _ in range(warmup):
+                fn(x)
+            ts = []
+            for _ in range(n):
+                flush.zero_()
+                a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn(x)
+                e.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(e))
+            return statistics.median(ts)
+
+        ms = timed(fused, steps)
+        ms_chain = timed(chain, 3)
+        gbs = alg_bytes / ms / 1e6
+        out[name] = dict(rows=rows, ms=ms, torch_chain_ms=ms_chain, algorithmic_bytes=alg_bytes,
+                         roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
+                                       frac=gbs / peaks["hbm_gbs"], traffic=None))
+        del x
+        torch.cuda.empty_cache()
+    return out
+
+
 def reference_gpu(torch, q, kv, idx, w1, w2, steps, warmup):
     import importlib.util
     path = os.path.join(ROOT, "oracle", "_ref", "mxdsa_ext.so")
@@ -386,6 +426,8 @@ def main():
             del q, idx
             torch.cuda.empty_cache()
             result["decode"] = decode_headline(torch, M, peaks, 20, 5)
+            torch.cuda.empty_cache()
+            result["pack"] = pack_headline(torch, peaks, 10, 3)
             result["gpu_launches_note"] = "prefill step = 1 attention kernel; decode step = attention + combine"
     if rank == 0:
         print(json.dumps(result))

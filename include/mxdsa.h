@@ -175,6 +175,53 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p);
 #define MXDSA_STATIC_SCRATCH_BYTES (32u << 20)
 int mxdsa_decode_fwd_static(const mxdsa_decode_params* p);
 
+/* ------------------------------------------------------------------------------------------
+ * Quantise-and-pack: the step in front of the attention entry points.  Stands in for the reference's
+ * Python packers (reference tests/mxfp8_test_utils.py: _quantize_groups :11-27, pack_dual_q64 :30-63,
+ * pack_dual_prefill_kv64 :66-78, pack_dual_decode_kv_pages :81-104), which the reference runs as a
+ * chain of torch kernels outside its timed path.  Byte-identical output for the same input values:
+ * scale = 2^ceil(log2(max(amax/448, 2^-126))), code = E4M3(clamp(x/scale, +-448)), each scale byte
+ * stored twice in the row's 16-byte slot.
+ * ------------------------------------------------------------------------------------------ */
+#define MXDSA_DTYPE_BF16 0
+#define MXDSA_DTYPE_F32 1
+
+/* Q rows.  One row = one (token, head): 512 values in, 528 bytes out.  Scale g is shared by dims
+ * [32g,32g+32) and [256+32g,256+32g+32).  paired_storage = 0 keeps the reference packer's natural
+ * byte order; 1 stores the bytes in the order [g][half][32] in which the attention kernel contracts
+ * them with K's natural order.  Strides of 0 mean densely packed (512 elements / 528 bytes).
+ * Rules: src, dst 16-byte aligned; row strides multiples of 16 bytes. */
+typedef struct mxdsa_pack_q_params {
+    int64_t rows;              /* tokens * 64 */
+    const void* src;           /* [rows][512] bf16 or f32 */
+    int32_t src_dtype;         /* MXDSA_DTYPE_* */
+    int64_t src_stride_row;    /* elements */
+    void* dst;                 /* u8 [rows][528] */
+    int64_t dst_stride_row;    /* bytes */
+    int32_t paired_storage;
+    void* stream;
+} mxdsa_pack_q_params;
+int mxdsa_pack_q(const mxdsa_pack_q_params* p);
+
+/* KV rows.  Scale g covers dims [64g,64g+64).  The output is a sequence of pages; a page holds
+ * rows_per_page*512 data bytes followed by rows_per_page 16-byte slots.  The prefill buffer is the
+ * one-page case (rows_per_page = rows = s_kv); decode pools use rows_per_page = page size and
+ * dst_stride_page = bytes between pages (0 = rows_per_page*528).  rows must be a multiple of
+ * rows_per_page. */
+typedef struct mxdsa_pack_kv_params {
+    int64_t rows;
+    const void* src;           /* [rows][512] bf16 or f32 */
+    int32_t src_dtype;
+    int64_t src_stride_row;    /* elements */
+    void* dst;
+    int32_t rows_per_page;
+    int64_t dst_stride_page;   /* bytes */
+    void* stream;
+} mxdsa_pack_kv_params;
+int mxdsa_pack_kv(const mxdsa_pack_kv_params* p);
+/* cudaError_t of the most recent failing launch of a pack kernel on this thread. */
+int mxdsa_pack_last_cuda_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -39,10 +39,18 @@ def build_lib(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIB, exist_ok=True)
     target = os.path.join(LIB, "libmxdsa.so")
     if force or _newer(target, _sources(".cu", ".cuh", ".h")):
-        cmd = [NVCC, *NVCC_FLAGS, "-shared", "-o", target, os.path.join(CSRC, "mxdsa_lib.cu"), "-lcudart"]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
-        subprocess.run(cmd, check=True)
+        # the attention kernels use fast-math intrinsics on purpose; the pack kernels need IEEE division
+        objs = []
+        for name, flags in (("mxdsa_lib.cu", NVCC_FLAGS), ("pack_kernels.cu", [f for f in NVCC_FLAGS if f != "--use_fast_math"])):
+            obj = os.path.join(LIB, name.replace(".cu", ".o"))
+            cmd = [NVCC, *flags, "-c", "-o", obj, os.path.join(CSRC, name)]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            subprocess.run(cmd, check=True)
+            objs.append(obj)
+        subprocess.run([NVCC, "-shared", "-o", target, *objs, "-lcudart"], check=True)
+        for obj in objs:
+            os.remove(obj)
     return target
 
 

@@ -14,8 +14,9 @@ LIB_PATH = os.path.join(_HERE, "lib", "libmxdsa.so")
 EXPORTS = (
     "mxdsa_status_string", "mxdsa_last_cuda_error", "mxdsa_device_fault", "mxdsa_prefill_fwd",
     "mxdsa_num_sm_parts", "mxdsa_decode_sched", "mxdsa_decode_workspace_bytes", "mxdsa_decode_fwd",
-    "mxdsa_decode_fwd_static",
+    "mxdsa_decode_fwd_static", "mxdsa_pack_q", "mxdsa_pack_kv", "mxdsa_pack_last_cuda_error",
 )
+DTYPE_BF16, DTYPE_F32 = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
 
 
@@ -58,6 +59,20 @@ class DecodeParams(C.Structure):
     ]
 
 
+class PackQParams(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int64), ("src", C.c_void_p), ("src_dtype", C.c_int32), ("src_stride_row", C.c_int64),
+        ("dst", C.c_void_p), ("dst_stride_row", C.c_int64), ("paired_storage", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
+class PackKVParams(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int64), ("src", C.c_void_p), ("src_dtype", C.c_int32), ("src_stride_row", C.c_int64),
+        ("dst", C.c_void_p), ("rows_per_page", C.c_int32), ("dst_stride_page", C.c_int64), ("stream", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -78,6 +93,9 @@ def lib() -> C.CDLL:
         L.mxdsa_decode_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
         L.mxdsa_decode_fwd.argtypes = [C.POINTER(DecodeParams)]
         L.mxdsa_decode_fwd_static.argtypes = [C.POINTER(DecodeParams)]
+        L.mxdsa_pack_q.argtypes = [C.POINTER(PackQParams)]
+        L.mxdsa_pack_kv.argtypes = [C.POINTER(PackKVParams)]
+        L.mxdsa_pack_last_cuda_error.restype = C.c_int
         _lib = L
     return _lib
 

@@ -46,6 +46,20 @@ def test_status_strings_and_argument_checks_need_no_gpu():
     assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 3   # q not 16-byte aligned -> MXDSA_ERR_ALIGN
     assert L.mxdsa_decode_workspace_bytes(128, 6, 24) == (128 + 24) * 6 * 64 * 513 * 4
     assert L.mxdsa_decode_workspace_bytes(0, 6, 24) == 0
+    # pack entry points: argument rules are checked before any CUDA call
+    assert L.mxdsa_pack_q(None) == 1 and L.mxdsa_pack_kv(None) == 1
+    q = capi.PackQParams(rows=0, src=16, src_dtype=capi.DTYPE_BF16, dst=16)
+    assert L.mxdsa_pack_q(ctypes.byref(q)) == 0          # nothing to do
+    q = capi.PackQParams(rows=2, src=16, src_dtype=7, dst=16)
+    assert L.mxdsa_pack_q(ctypes.byref(q)) == 2          # unknown dtype
+    q = capi.PackQParams(rows=2, src=24, src_dtype=capi.DTYPE_F32, dst=16)
+    assert L.mxdsa_pack_q(ctypes.byref(q)) == 3          # source not 16-byte aligned
+    q = capi.PackQParams(rows=2, src=16, src_dtype=capi.DTYPE_BF16, dst=16, dst_stride_row=520)
+    assert L.mxdsa_pack_q(ctypes.byref(q)) == 3          # row stride below 528 / not a multiple of 16
+    k = capi.PackKVParams(rows=10, src=16, src_dtype=capi.DTYPE_BF16, dst=16, rows_per_page=4)
+    assert L.mxdsa_pack_kv(ctypes.byref(k)) == 2         # rows not a multiple of the page size
+    k = capi.PackKVParams(rows=8, src=16, src_dtype=capi.DTYPE_BF16, dst=16, rows_per_page=0)
+    assert L.mxdsa_pack_kv(ctypes.byref(k)) == 2
 
 
 def test_extension_module_exposes_the_reference_entry_points():
