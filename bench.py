@@ -304,6 +304,14 @@ def run_profile_case(which: str):
         for _ in range(3):
             M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, 512 ** -0.5, w1, w2, None, None)
         case = {"kernel": "mxdsa_attn_kernel<prefill,128>", "s_q": s_q, "kv_len": S_KV, "topk": TOPK}
+    elif which == "pack":
+        from mxdsa_b200 import quantize as Z
+        x = torch.randn((4096, HEADS, 512), device="cuda").bfloat16()     # 268 MB in, 138 MB out
+        kv = torch.randn((262144, 1, 512), device="cuda").bfloat16()
+        for _ in range(3):
+            Z.pack_dual_q64(x)
+            Z.pack_dual_prefill_kv64(kv)
+        case = {"kernel": "mxdsa_pack_rows_kernel<bf16, Q> and <bf16, KV>", "rows": 262144}
     else:
         from mxdsa_b200 import packing as P
         b, s_q, extra = 32, 6, 4096                    # 32 requests x 8.65 MB of private extra pages = 277 MB
@@ -334,7 +342,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--sq", type=int, default=S_Q, help="query tokens per GPU (default: the headline 65536)")
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu baseline, decode and comparator")
-    ap.add_argument("--profile-case", choices=["prefill", "decode"], default=None,
+    ap.add_argument("--profile-case", choices=["prefill", "decode", "pack"], default=None,
                     help="launch a small case of one kernel a few times and exit (for profiler captures; no timing)")
     args = ap.parse_args()
     if args.profile_case:
