@@ -62,8 +62,8 @@ int mxdsa_device_fault(void* stream);
  *
  * Query tokens 2p and 2p+1 share index row p.  Key j of row p is attended when
  * 0 <= indices[p][j] < s_kv and j < topk_length[p] (topk when topk_length is NULL).
- * Rules: s_q > 0 and even; topk > 0 and a multiple of 64; q, kv 16-byte aligned;
- * stride_q_token a multiple of 16 bytes.
+ * Rules: s_q > 0 and even; topk > 0 and a multiple of 64; q, kv 16-byte aligned; out 32-byte
+ * aligned; stride_q_token a multiple of 16 bytes.
  * ------------------------------------------------------------------------------------------ */
 typedef struct mxdsa_prefill_params {
     int32_t s_q, s_kv, topk;
@@ -122,7 +122,8 @@ size_t mxdsa_decode_workspace_bytes(int b, int s_q, int num_sm_parts);
  * follow index row p of that request, as in the reference (decode_kernel.cuh:108, 554-558).
  * Key j is attended when indices[..][j] != -1 and j < topk_length[request].
  * Rules: topk > 0 and a multiple of 64; page strides multiples of 512 bytes; extra_* all present
- * or all absent (extra_topk_length optional); pointers 16-byte aligned. */
+ * or all absent (extra_topk_length optional); pointers 16-byte aligned, out and workspace 32-byte
+ * aligned. */
 typedef struct mxdsa_decode_params {
     int32_t b, s_q, topk, extra_topk;
     float sm_scale;
@@ -147,7 +148,7 @@ typedef struct mxdsa_decode_params {
     const int32_t* sched_meta;        /* [num_sm_parts][8] from mxdsa_decode_sched */
     const int32_t* num_splits;        /* [b+1] */
     int32_t num_sm_parts;
-    void* workspace;                  /* mxdsa_decode_workspace_bytes(...) bytes, 16-byte aligned */
+    void* workspace;                  /* mxdsa_decode_workspace_bytes(...) bytes, 32-byte aligned */
     size_t workspace_bytes;
     void* stream;
 } mxdsa_decode_params;

@@ -342,6 +342,10 @@ __device__ __noinline__ void rescale_o(uint32_t lane_addr, float f) {
     }
     tmem_wait_st();
 }
+// one 32-byte store (a whole sector); the address must be 32-byte aligned
+__device__ __forceinline__ void st_global_32B(void* dst, const unsigned long long (&u)[4]) {
+    asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(dst), "l"(u[0]), "l"(u[1]), "l"(u[2]), "l"(u[3]) : "memory");
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -1102,13 +1106,19 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     tmem_ld32(lane_addr + kColO + grp * 128 + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
+                        // 32 columns -> 64 bytes of bf16: two 32-byte stores per lane (whole sectors; sixteen-byte
+                        // stores from 32 lanes to 32 rows touch every sector twice and took twice as long)
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            __nv_bfloat162 v[4];
+                        for (int i = 0; i < 32; i += 16) {
+                            unsigned long long u[4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                v[j] = __floats2bfloat162_rn(o[i + 2 * j] * oscale, o[i + 2 * j + 1] * oscale);
-                            *reinterpret_cast<uint4*>(dst + c + i) = *reinterpret_cast<uint4*>(v);
+                            for (int j = 0; j < 4; ++j) {
+                                const __nv_bfloat162 lo = __floats2bfloat162_rn(o[i + 4 * j] * oscale, o[i + 4 * j + 1] * oscale);
+                                const __nv_bfloat162 hi = __floats2bfloat162_rn(o[i + 4 * j + 2] * oscale, o[i + 4 * j + 3] * oscale);
+                                u[j] = (unsigned long long)(*reinterpret_cast<const uint32_t*>(&lo)) |
+                                       ((unsigned long long)(*reinterpret_cast<const uint32_t*>(&hi)) << 32);
+                            }
+                            st_global_32B(dst + c + i, u);
                         }
                     }
                 }
@@ -1121,9 +1131,14 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            *reinterpret_cast<float4*>(dst + c + i) =
-                                make_float4(o[i] * oscale, o[i + 1] * oscale, o[i + 2] * oscale, o[i + 3] * oscale);
+                        for (int i = 0; i < 32; i += 8) {
+                            unsigned long long u[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                u[j] = (unsigned long long)__float_as_uint(o[i + 2 * j] * oscale) |
+                                       ((unsigned long long)__float_as_uint(o[i + 2 * j + 1] * oscale) << 32);
+                            st_global_32B(dst + c + i, u);
+                        }
                     }
                 }
             }

@@ -71,6 +71,7 @@ int device_info(DeviceInfo** out) {
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }   // outputs: 32-byte stores
 
 // 5-D map over packed Q: {128 bytes, 64 heads, 4 chunks, tokens, requests}; one box = the 512 data
 // bytes of all 64 heads of one token, landing as [chunk][head][128 B].
@@ -306,7 +307,7 @@ int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     if (p->s_q <= 0 || (p->s_q & 1) || p->s_kv <= 0 || p->topk <= 0 || (p->topk % 64) != 0) return MXDSA_ERR_SHAPE;
     if (p->stride_q_token < (int64_t)MXDSA_HEADS * MXDSA_ROW_BYTES || p->stride_indices_pair < p->topk)
         return MXDSA_ERR_SHAPE;
-    if (!aligned16(p->q) || !aligned16(p->kv) || (p->stride_q_token & 15) || !aligned16(p->out))
+    if (!aligned16(p->q) || !aligned16(p->kv) || (p->stride_q_token & 15) || !aligned32(p->out))
         return MXDSA_ERR_ALIGN;
     DeviceInfo* d = nullptr;
     int st = device_info(&d);
@@ -391,11 +392,11 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
                       p->stride_extra_kv_block < (int64_t)p->extra_page_block_size * MXDSA_ROW_BYTES))
         return MXDSA_ERR_ALIGN;
     if (!aligned16(p->q) || !aligned16(p->kv) || (has_extra && !aligned16(p->extra_kv)) || (p->stride_q_s & 15) ||
-        (p->stride_q_b & 15) || !aligned16(p->out))
+        (p->stride_q_b & 15) || !aligned32(p->out))
         return MXDSA_ERR_ALIGN;
     if (p->stride_q_s < (int64_t)MXDSA_HEADS * MXDSA_ROW_BYTES) return MXDSA_ERR_SHAPE;
     const size_t need = mxdsa_decode_workspace_bytes(p->b, p->s_q, p->num_sm_parts);
-    if (p->workspace == nullptr || p->workspace_bytes < need || !aligned16(p->workspace)) return MXDSA_ERR_WORKSPACE;
+    if (p->workspace == nullptr || p->workspace_bytes < need || !aligned32(p->workspace)) return MXDSA_ERR_WORKSPACE;
     DeviceInfo* d = nullptr;
     int st = device_info(&d);
     if (st != MXDSA_OK) return st;

@@ -216,3 +216,46 @@ def test_decode_properties_at_headline_shape():
     # so compare at the "ideal math" tolerance
     assert O.cosine(o, ro) >= 0.9995
     assert np.abs(l - rl).max() <= 1e-3
+
+
+def test_entry_points_are_cuda_graph_capturable():
+    """The reference's benchmark captures its calls in CUDA graphs (reference tests/benchmark.py:44-46):
+    both operators must record into a graph without synchronising and replay to the eager results."""
+    import mxdsa_b200 as M
+    from mxdsa_b200 import packing as P
+    g = torch.Generator(device="cuda").manual_seed(21)
+    q = P.pack_dual_q64(torch.randn(32, 64, 512, device="cuda", generator=g))[0]
+    kvf, w1, w2 = P.make_rank1_kv((1024, 1), device="cuda", generator=g)
+    kv = P.pack_dual_prefill_kv64(kvf)[0]
+    idx = torch.stack([torch.randperm(1024, device="cuda", generator=g)[:512] for _ in range(16)]).int().view(16, 1, 512)
+    eager = M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, 512 ** -0.5, w1, w2, None, None)
+    # decode inputs: 4 requests, 2 pages of 64 each
+    qd = P.pack_dual_q64(torch.randn(4 * 2, 64, 512, device="cuda", generator=g))[0].view(4, 2, 64, 528)
+    pool = P.pack_dual_decode_kv_pages(P.make_rank1_kv((8, 64, 1), device="cuda", generator=g)[0])[0]
+    didx = (torch.rand(8, 128, device="cuda", generator=g).argsort(1).int().view(4, 2, 128)
+            + 128 * torch.arange(4, device="cuda", dtype=torch.int32)[:, None, None]).contiguous()
+    first = M.dual_mxfp8_sparse_decode_fwd(qd, pool, didx, None, None, None, None, None, None, None, 512, 512,
+                                           512 ** -0.5, w1, w2)
+    meta, splits = first[2], first[3]
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):     # warm-up on the capture stream, as torch's graph notes ask
+        M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, 512 ** -0.5, w1, w2, None, None)
+        M.dual_mxfp8_sparse_decode_fwd(qd, pool, didx, None, None, meta, splits, None, None, None, 512, 512, 512 ** -0.5,
+                                       w1, w2)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        cap = M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, 512 ** -0.5, w1, w2, None, None)
+        capd = M.dual_mxfp8_sparse_decode_fwd(qd, pool, didx, None, None, meta, splits, None, None, None, 512, 512,
+                                              512 ** -0.5, w1, w2)
+    for _ in range(2):
+        for t in (*cap, capd[0], capd[1]):
+            t.zero_() if t.is_contiguous() else t.fill_(0)
+        graph.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(cap, eager):
+            assert torch.equal(a, b)
+        assert torch.equal(capd[0], first[0]) and torch.equal(capd[1], first[1])
+    M.device_fault()
