@@ -259,3 +259,25 @@ def test_entry_points_are_cuda_graph_capturable():
             assert torch.equal(a, b)
         assert torch.equal(capd[0], first[0]) and torch.equal(capd[1], first[1])
     M.device_fault()
+
+
+def test_host_buffer_prefill_matches_device_call():
+    """mxdsa_b200.host.prefill_from_host (chunked, three streams) writes what one device call returns."""
+    import mxdsa_b200 as M
+    from mxdsa_b200 import host, packing as P
+    g = torch.Generator(device="cuda").manual_seed(31)
+    s_q = 6 * 64 + 2          # not a multiple of the chunk: ragged last chunk
+    q = P.pack_dual_q64(torch.randn(s_q, 64, 512, device="cuda", generator=g))[0]
+    kvf, w1, w2 = P.make_rank1_kv((2048, 1), device="cuda", generator=g)
+    kv = P.pack_dual_prefill_kv64(kvf)[0]
+    idx = torch.stack([torch.randperm(2048, device="cuda", generator=g)[:256] for _ in range(s_q // 2)]).int().view(-1, 1, 256)
+    want = M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, 512 ** -0.5, w1, w2, None, None)
+    hq, hkv, hidx = q.cpu().pin_memory(), kv.cpu().pin_memory(), idx.cpu().pin_memory()
+    h_out = torch.zeros((s_q, 64, 512), dtype=torch.bfloat16).pin_memory()
+    h_mxl = torch.zeros((s_q, 64), dtype=torch.float32).pin_memory()
+    h_lse = torch.zeros((s_q, 64), dtype=torch.float32).pin_memory()
+    for _ in range(2):
+        host.prefill_from_host(hq, hkv, hidx, 512 ** -0.5, w1, w2, h_out, h_mxl, h_lse, chunk_tokens=64)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(h_out, want[0].cpu()) and torch.equal(h_mxl, want[1].cpu()) and torch.equal(h_lse, want[2].cpu())
+        h_out.zero_()
