@@ -155,6 +155,24 @@ typedef struct mxdsa_decode_params {
 
 int mxdsa_decode_fwd(const mxdsa_decode_params* p);
 
+/* The combine step alone.  Stands in for run_flash_mla_combine_kernel<bf16> (reference
+ * csrc/split_kv/combine.cu:415-448, CombineParams params.h:240-260) for callers that sequence the
+ * attention and the combine themselves; mxdsa_decode_fwd already runs it.  `workspace` is the buffer
+ * an earlier mxdsa_decode_fwd with the same b, s_q, num_sm_parts, sched_meta and num_splits filled.
+ * Only requests that the schedule splits over several parts are written (out and lse). */
+typedef struct mxdsa_combine_params {
+    int32_t b, s_q, num_sm_parts;
+    const int32_t* sched_meta;        /* [num_sm_parts][8] */
+    const int32_t* num_splits;        /* [b+1] */
+    const void* workspace;            /* mxdsa_decode_workspace_bytes(...) bytes, 32-byte aligned */
+    size_t workspace_bytes;
+    const float* attn_sink;           /* [64] or NULL */
+    void* out;                        /* bf16 [b][s_q][64][512], 32-byte aligned */
+    float* lse;                       /* [b][s_q][64] */
+    void* stream;
+} mxdsa_combine_params;
+int mxdsa_decode_combine(const mxdsa_combine_params* p);
+
 /* Decode without caller-provided scratch.  (No counterpart in the reference, whose binding
  * allocates its scratch with torch on every call.)
  *

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libmxdsa.so")
 EXPORTS = (
     "mxdsa_status_string", "mxdsa_last_cuda_error", "mxdsa_device_fault", "mxdsa_prefill_fwd",
     "mxdsa_num_sm_parts", "mxdsa_decode_sched", "mxdsa_decode_workspace_bytes", "mxdsa_decode_fwd",
-    "mxdsa_decode_fwd_static", "mxdsa_pack_q", "mxdsa_pack_kv", "mxdsa_pack_last_cuda_error",
+    "mxdsa_decode_fwd_static", "mxdsa_decode_combine", "mxdsa_pack_q", "mxdsa_pack_kv", "mxdsa_pack_last_cuda_error",
 )
 DTYPE_BF16, DTYPE_F32 = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
@@ -59,6 +59,15 @@ class DecodeParams(C.Structure):
     ]
 
 
+class CombineParams(C.Structure):
+    _fields_ = [
+        ("b", C.c_int32), ("s_q", C.c_int32), ("num_sm_parts", C.c_int32),
+        ("sched_meta", C.c_void_p), ("num_splits", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("attn_sink", C.c_void_p),
+        ("out", C.c_void_p), ("lse", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
 class PackQParams(C.Structure):
     _fields_ = [
         ("rows", C.c_int64), ("src", C.c_void_p), ("src_dtype", C.c_int32), ("src_stride_row", C.c_int64),
@@ -93,6 +102,7 @@ def lib() -> C.CDLL:
         L.mxdsa_decode_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
         L.mxdsa_decode_fwd.argtypes = [C.POINTER(DecodeParams)]
         L.mxdsa_decode_fwd_static.argtypes = [C.POINTER(DecodeParams)]
+        L.mxdsa_decode_combine.argtypes = [C.POINTER(CombineParams)]
         L.mxdsa_pack_q.argtypes = [C.POINTER(PackQParams)]
         L.mxdsa_pack_kv.argtypes = [C.POINTER(PackKVParams)]
         L.mxdsa_pack_last_cuda_error.restype = C.c_int

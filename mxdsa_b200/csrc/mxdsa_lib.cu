@@ -463,6 +463,30 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
 }
 
 // ------------------------------------------------------------------------------------------
+// The combine step on its own: merges the split partials that an earlier mxdsa_decode_fwd (or any
+// producer of the same workspace layout) left in `workspace`.  mxdsa_decode_fwd runs it itself; this
+// entry point exists for callers that sequence attention and combine separately, as the reference's
+// binding does (run_flash_mla_combine_kernel, reference csrc/split_kv/combine.cu:415-448).
+// ------------------------------------------------------------------------------------------
+extern "C" int mxdsa_decode_combine(const mxdsa_combine_params* p) {
+    if (p == nullptr || p->sched_meta == nullptr || p->num_splits == nullptr || p->out == nullptr || p->lse == nullptr)
+        return MXDSA_ERR_NULL;
+    if (p->b <= 0 || p->s_q <= 0 || p->num_sm_parts <= 0) return MXDSA_ERR_SHAPE;
+    const size_t need = mxdsa_decode_workspace_bytes(p->b, p->s_q, p->num_sm_parts);
+    if (p->workspace == nullptr || p->workspace_bytes < need || !aligned32(p->workspace)) return MXDSA_ERR_WORKSPACE;
+    if (!aligned32(p->out)) return MXDSA_ERR_ALIGN;
+    const size_t slots = (size_t)(p->b + p->num_sm_parts) * p->s_q * MXDSA_HEADS;
+    const float* o_accum = static_cast<const float*>(p->workspace);
+    const float* lse_accum = o_accum + slots * MXDSA_DIM;
+    const dim3 cgrid(p->num_sm_parts * p->s_q, MXDSA_HEADS / 8, 1);
+    mxdsa_combine_kernel<<<cgrid, 256, 0, static_cast<cudaStream_t>(p->stream)>>>(
+        p->b, p->s_q, p->num_sm_parts, p->sched_meta, p->num_splits, o_accum, lse_accum, p->attn_sink,
+        static_cast<__nv_bfloat16*>(p->out), p->lse);
+    MX_CUDA(cudaGetLastError());
+    return MXDSA_OK;
+}
+
+// ------------------------------------------------------------------------------------------
 // Decode for callers that cannot allocate device memory.
 //
 // Some hosts of this library hand out no allocator at all: a serving process that gives every
