@@ -11,18 +11,21 @@
 //   accumulators live in tensor memory: per CTA 128 lanes x (256 O + 2 x 64 P) columns; lane L
 //   holds row L%64, and column half L/64 (P: keys 64*(L/64).., O: dims 256*(L/64)..).
 //
-// Roles (warp-specialised, 20 warps per CTA, 96 registers per thread)
-//   warps 0-3   K producers: read key indices and copy the selected rows of this CTA's 64 keys
+// Roles (warp-specialised, 20 warps per CTA; 96 registers per thread at launch, re-balanced in prefill to
+// 64 for the copy and control warps and 144 for the softmax warps)
+//   warps 0-3   K producers (one instruction stream with the V producers): read key indices and copy the
+//               selected rows of this CTA's 64 keys
 //               into a 2-deep K ring with 16-byte cp.async; one warp instruction moves one
 //               512-byte row straight into the 128-byte-swizzled operand layout.  Measured on a
 //               B200 this path sustains ~40 B/clk/SM of random 512-byte rows from L2 with eight
 //               issuing warps (about 9 B/clk per warp), against ~21 B/clk/SM for TMA gather4.
 //   warps 4-7   V producers: same for the 256-byte halves of all 128 keys (3-deep V ring)
 //   warp 8      CTA 0: QK issuer for even tiles      CTA 1: relays "K rows landed" to CTA 0
+//               (issuers run as converged warps, one elected lane issues fully unrolled MMAs)
 //   warp 9      CTA 0: QK issuer for odd tiles       (each with its own P buffer and scale columns)
 //   warp 10     CTA 0: PV issuer                     CTA 1: relays "V rows landed" to CTA 0
 //   warp 11     operand stager: Q tile TMA + Q scale rows (per pair); K scale rows, key token
-//               scales and validity bits (per tile)
+//               scales and validity bits (per tile), index and slot loads two tiles deep
 //   warps 12-19 softmax: two groups of four warps take alternate tiles (each thread one row and one
 //               64-key half of its tile): P -> registers, running max with lazy rescale handed
 //               from group to group, exp2, token-scale, per-32-key UE8M0 requantisation to E4M3
@@ -41,7 +44,7 @@
 //     max_logits = true max * ln2 [prefill_kernel.cuh:988-1019]; decode splits write O/l and
 //     log2(l)+m for the combine step [decode_kernel.cuh:199-218].
 //
-// Every wait is bounded (see sm100_ptx.cuh); on expiry the pair raises `fault` and leaves through
+// Every wait is bounded (the loops are written out at the wait sites below); on expiry the pair raises `fault` and leaves through
 // the normal tear-down.
 #pragma once
 
