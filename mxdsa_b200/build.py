@@ -48,7 +48,8 @@ def build_lib(force: bool = False, verbose: bool = False) -> str:
                 cmd.insert(1, "-Xptxas=-v")
             subprocess.run(cmd, check=True)
             objs.append(obj)
-        subprocess.run([NVCC, "-shared", "-o", target, *objs, "-lcudart"], check=True)
+        subprocess.run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", target, *objs, "-lcudart"],
+                       check=True)
         for obj in objs:
             os.remove(obj)
     return target
