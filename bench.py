@@ -128,7 +128,7 @@ def time_steps(torch, fn, steps, warmup, dist=None):
     return evs[0].elapsed_time(evs[steps]), per
 
 
-def cpu_baseline(torch, q, kv, idx, w1, w2, target_s=12.0):
+def cpu_baseline(torch, q, kv, idx, w1, w2, target_s=20.0):
     """torch dequantise-and-gather on host cores over a bounded sample of the same workload."""
     from oracle import cpu_baseline as cb
     cores = os.cpu_count() or 1
@@ -138,7 +138,7 @@ def cpu_baseline(torch, q, kv, idx, w1, w2, target_s=12.0):
     t0 = time.time()
     cb.prefill_cpu(q[:tokens].cpu(), k, v, idx[:tokens // 2].cpu(), 512 ** -0.5, cores)
     probe = max(time.time() - t0, 1e-3)
-    tokens = int(min(16384, max(32, 2 * round(tokens * target_s / probe / 2))))
+    tokens = int(min(32768, max(32, 2 * round(tokens * target_s / probe / 2))))
     qs, ids = q[:tokens].cpu(), idx[:tokens // 2].cpu()
     t0 = time.time()
     cb.prefill_cpu(qs, k, v, ids, 512 ** -0.5, cores)
