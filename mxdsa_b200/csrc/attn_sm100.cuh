@@ -316,9 +316,6 @@ __device__ __forceinline__ float2 f2_add(float2 a, float2 b) {
 
 // 16-byte asynchronous copy global -> shared; `bytes` = 16 copies, 0 writes zeros.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
-#ifdef MXDSA_EXP_NOCOPY
-    return;
-#endif
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 // one arrival on `bar` once all cp.async issued so far by this thread have landed
@@ -969,24 +966,12 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #pragma unroll 1
                 for (int g = 0; g < 2; ++g) {
                     uint32_t s8[8];
-#ifdef MXDSA_EXP_NOSOFTMAX
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) s8[i] = 0x38383838u;
-                    uint32_t e = 0x7f;
-                    if (false)
-#else
                     uint32_t e;
-#endif
                     {
                         float am = 0.f;
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
-#ifdef MXDSA_EXP_NOTOK
-                            const float4 tk = make_float4(1.f, 1.f, 1.f, 1.f);
-                            (void)tok4;
-#else
                             const float4 tk = tok4[g * 8 + i / 4];
-#endif
                             float2 a = f2_fma(make_float2(x[i], x[i + 1]), scale2, negm2);
                             float2 c = f2_fma(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
                             a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
