@@ -383,9 +383,9 @@ def main():
     achieved = prefill_flops(s_q, TOPK) / kern_ms / 1e9
     peak = 2.0 * peaks["bf16_tflops_sustained"]
     # DRAM traffic of one launch: dram__bytes_read + dram__bytes_write of this kernel from the ncu capture
-    # of `bench.py --profile-case prefill` (s_q = 4096: 180.9 MB read of which 8.65 MB is the KV that
-    # does not grow with s_q, 218.0 MB written), scaled by the query tokens of this launch.
-    traffic = ((180.9e6 - 8.65e6) + 218.0e6) * (s_q / 4096.0) + 8.65e6
+    # of `bench.py --profile-case prefill` (s_q = 4096: 181.2 MB read of which 8.65 MB is the KV that
+    # does not grow with s_q, 221.7 MB written), scaled by the query tokens of this launch.
+    traffic = ((181.2e6 - 8.65e6) + 221.7e6) * (s_q / 4096.0) + 8.65e6
     roofline = dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
                     traffic=traffic, traffic_unit="bytes per launch (ncu small-case capture scaled by query tokens)",
                     algorithmic_bytes=s_q * (HEADS * 528 + TOPK * 2 + HEADS * 512 * 2 + HEADS * 8) + S_KV * 528,
