@@ -159,7 +159,7 @@ def run_reference_arm(args):
     from oracle import cpu_baseline as cb
     torch.manual_seed(0)
     cores = os.cpu_count() or 1
-    tokens = 64
+    tokens = 2048      # upper bound of the per-step sample; cut down below if the box is slow
     q = P.pack_dual_q64(torch.randn(tokens, HEADS, 512))[0]
     kvf, w1, w2 = P.make_rank1_kv((S_KV, 1))
     kv = P.pack_dual_prefill_kv64(kvf)[0]
