@@ -274,6 +274,42 @@ def pack_headline(torch, peaks, steps, warmup):
     return out
 
 
+def topk_headline(torch, peaks, steps, warmup):
+    """The producer of the path's other input: index selection for 8192 query pairs (score rows of both
+    tokens, 16 384 keys each, 1.07 GB read) -> 4096 ascending indices per pair, against the HBM roof;
+    torch.topk + sort on the pair-merged scores is timed beside it."""
+    from mxdsa_b200.indexer import select_topk_indices
+    g = torch.Generator(device="cuda").manual_seed(11)
+    pairs, s_kv, topk = 8192, S_KV, TOPK
+    scores = torch.randn((2 * pairs, s_kv), device="cuda", generator=g)
+    alg_bytes = 2 * pairs * s_kv * 4 + pairs * topk * 4
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def chain(x):
+        return torch.topk(torch.maximum(x[0::2], x[1::2]), topk, dim=1).indices.sort(dim=1).values.int()
+
+    def timed(fn, n):
+        for _ in range(warmup):
+            fn(scores)
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn(scores)
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(e))
+        return statistics.median(ts)
+
+    ms = timed(lambda x: select_topk_indices(x, topk, pair=True), steps)
+    ms_chain = timed(chain, 3)
+    gbs = alg_bytes / ms / 1e6
+    return dict(pairs=pairs, s_kv=s_kv, topk=topk, ms=ms, torch_chain_ms=ms_chain, algorithmic_bytes=alg_bytes,
+                roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
+                              frac=gbs / peaks["hbm_gbs"], traffic=None))
+
+
 def reference_gpu(torch, q, kv, idx, w1, w2, steps, warmup):
     import importlib.util
     path = os.path.join(ROOT, "oracle", "_ref", "mxdsa_ext.so")
@@ -304,6 +340,12 @@ def run_profile_case(which: str):
         for _ in range(3):
             M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, 512 ** -0.5, w1, w2, None, None)
         case = {"kernel": "mxdsa_attn_kernel<prefill,128>", "s_q": s_q, "kv_len": S_KV, "topk": TOPK}
+    elif which == "topk":
+        from mxdsa_b200.indexer import select_topk_indices
+        scores = torch.randn((2 * 2048, S_KV), device="cuda")              # 268 MB of scores
+        for _ in range(3):
+            select_topk_indices(scores, TOPK, pair=True)
+        case = {"kernel": "mxdsa_topk_rows_kernel<2>", "pairs": 2048, "s_kv": S_KV, "topk": TOPK}
     elif which == "pack":
         from mxdsa_b200 import quantize as Z
         x = torch.randn((4096, HEADS, 512), device="cuda").bfloat16()     # 268 MB in, 138 MB out
@@ -342,7 +384,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--sq", type=int, default=S_Q, help="query tokens per GPU (default: the headline 65536)")
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu baseline, decode and comparator")
-    ap.add_argument("--profile-case", choices=["prefill", "decode", "pack"], default=None,
+    ap.add_argument("--profile-case", choices=["prefill", "decode", "pack", "topk"], default=None,
                     help="launch a small case of one kernel a few times and exit (for profiler captures; no timing)")
     args = ap.parse_args()
     if args.profile_case:
@@ -437,6 +479,7 @@ def main():
             result["decode"] = decode_headline(torch, M, peaks, 20, 5)
             torch.cuda.empty_cache()
             result["pack"] = pack_headline(torch, peaks, 10, 3)
+            result["topk_select"] = topk_headline(torch, peaks, 10, 3)
             result["gpu_launches_note"] = "prefill step = 1 attention kernel; decode step = attention + combine"
     if rank == 0:
         print(json.dumps(result))

@@ -241,6 +241,36 @@ int mxdsa_pack_kv(const mxdsa_pack_kv_params* p);
 /* cudaError_t of the most recent failing launch of a pack kernel on this thread. */
 int mxdsa_pack_last_cuda_error(void);
 
+/* ------------------------------------------------------------------------------------------
+ * Index selection: scores -> the int32 index rows (and valid lengths) that mxdsa_prefill_fwd and
+ * mxdsa_decode_fwd consume.  The reference has no producer for `indices`; its callers define the
+ * conventions this follows (reference tests/benchmark.py:119-147: one row per pair of query tokens,
+ * -1 entries never attended, decode pools addressed by request * pool_len + slot; csrc/api/binding.cpp
+ * :12-15 and csrc/api/sparse_attn_decode.h:13-20 for shapes and topk_length).
+ *
+ * Row r takes the min(topk, candidates) highest-scoring keys among j < lengths[r] (all s_kv when
+ * lengths is NULL); a score that is NaN or -inf is no candidate; ties go to the smaller j.  With
+ * group = 2 the score of key j is the larger of score rows 2r and 2r+1 (the two tokens of a pair).
+ * The selected j (+ row_offset[r] when given) are written in ascending order, then -1 up to topk;
+ * topk_length[r] = the number selected.  Exact and deterministic.
+ * Rules: s_kv a multiple of 4; scores 16-byte aligned, score_stride a multiple of 4 elements;
+ * strides of 0 mean densely packed.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mxdsa_topk_params {
+    const float* scores;        /* f32 [rows*group][s_kv]                         */
+    int64_t score_stride;       /* elements between score rows                    */
+    const int32_t* lengths;     /* [rows] or NULL                                 */
+    const int32_t* row_offset;  /* [rows] or NULL: added to every selected index  */
+    int32_t* indices;           /* out [rows][topk]                               */
+    int64_t index_stride;       /* elements between index rows                    */
+    int32_t* topk_length;       /* out [rows] or NULL                             */
+    int32_t rows, group, s_kv, topk;
+    void* stream;
+} mxdsa_topk_params;
+int mxdsa_topk_select(const mxdsa_topk_params* p);
+/* cudaError_t of the most recent failing launch of the selection kernel on this thread. */
+int mxdsa_topk_last_cuda_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -39,9 +39,10 @@ def build_lib(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIB, exist_ok=True)
     target = os.path.join(LIB, "libmxdsa.so")
     if force or _newer(target, _sources(".cu", ".cuh", ".h")):
-        # the attention kernels use fast-math intrinsics on purpose; the pack kernels need IEEE division
+        # the attention kernels use fast-math intrinsics on purpose; the pack and selection kernels need IEEE arithmetic
         objs = []
-        for name, flags in (("mxdsa_lib.cu", NVCC_FLAGS), ("pack_kernels.cu", [f for f in NVCC_FLAGS if f != "--use_fast_math"])):
+        ieee = [f for f in NVCC_FLAGS if f != "--use_fast_math"]
+        for name, flags in (("mxdsa_lib.cu", NVCC_FLAGS), ("pack_kernels.cu", ieee), ("topk_kernels.cu", ieee)):
             obj = os.path.join(LIB, name.replace(".cu", ".o"))
             cmd = [NVCC, *flags, "-c", "-o", obj, os.path.join(CSRC, name)]
             if verbose:

@@ -15,6 +15,7 @@ EXPORTS = (
     "mxdsa_status_string", "mxdsa_last_cuda_error", "mxdsa_device_fault", "mxdsa_prefill_fwd",
     "mxdsa_num_sm_parts", "mxdsa_decode_sched", "mxdsa_decode_workspace_bytes", "mxdsa_decode_fwd",
     "mxdsa_decode_fwd_static", "mxdsa_decode_combine", "mxdsa_pack_q", "mxdsa_pack_kv", "mxdsa_pack_last_cuda_error",
+    "mxdsa_topk_select", "mxdsa_topk_last_cuda_error",
 )
 DTYPE_BF16, DTYPE_F32 = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
@@ -82,6 +83,14 @@ class PackKVParams(C.Structure):
     ]
 
 
+class TopkParams(C.Structure):
+    _fields_ = [
+        ("scores", C.c_void_p), ("score_stride", C.c_int64), ("lengths", C.c_void_p), ("row_offset", C.c_void_p),
+        ("indices", C.c_void_p), ("index_stride", C.c_int64), ("topk_length", C.c_void_p),
+        ("rows", C.c_int32), ("group", C.c_int32), ("s_kv", C.c_int32), ("topk", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -106,6 +115,8 @@ def lib() -> C.CDLL:
         L.mxdsa_pack_q.argtypes = [C.POINTER(PackQParams)]
         L.mxdsa_pack_kv.argtypes = [C.POINTER(PackKVParams)]
         L.mxdsa_pack_last_cuda_error.restype = C.c_int
+        L.mxdsa_topk_select.argtypes = [C.POINTER(TopkParams)]
+        L.mxdsa_topk_last_cuda_error.restype = C.c_int
         _lib = L
     return _lib
 

@@ -646,6 +646,37 @@ def combine_ref(lse_accum: np.ndarray, o_accum: np.ndarray, sink: Optional[np.nd
 
 
 # --------------------------------------------------------------------------------------
+# index selection (the producer of `indices`)
+# --------------------------------------------------------------------------------------
+def topk_select_ref(scores: np.ndarray, topk: int, lengths: Optional[np.ndarray] = None, pair: bool = False,
+                    row_offset: Optional[np.ndarray] = None) -> Tuple[np.ndarray, np.ndarray]:
+    """Index selection feeding ``indices`` (no counterpart in the reference: "parity unpinned"; the
+    definition follows the conventions of the reference's callers, tests/benchmark.py:119-147 --
+    one row per pair, -1 never attended, pool offsets added to the slot index).
+
+    scores f32 [n, s_kv] -> (indices i32 [rows, topk], topk_length i32 [rows]); rows = n/2 with
+    ``pair`` (a key's score = the larger of the two tokens', NaN on one side ignored).  Row r keeps the
+    min(topk, candidates) best keys among j < lengths[r]; NaN / -inf are no candidates; ties go to the
+    smaller j (stable sort); selected indices ascending (+ row_offset[r]), then -1.
+    """
+    s = np.asarray(scores, dtype=np.float32)
+    if pair:
+        s = np.fmax(s[0::2], s[1::2])
+    rows, s_kv = s.shape
+    idx = np.full((rows, topk), -1, dtype=np.int32)
+    cnt = np.zeros((rows,), dtype=np.int32)
+    for r in range(rows):
+        n = s_kv if lengths is None else int(min(max(int(lengths[r]), 0), s_kv))
+        row = s[r, :n]
+        cand = np.nonzero(~np.isnan(row) & (row != -np.inf))[0]
+        order = cand[np.argsort(-row[cand].astype(np.float64), kind="stable")]   # descending score, ascending j in ties
+        keep = np.sort(order[:topk])
+        cnt[r] = keep.size
+        idx[r, :keep.size] = keep + (0 if row_offset is None else int(row_offset[r]))
+    return idx, cnt
+
+
+# --------------------------------------------------------------------------------------
 # error measures used by the tests (north-star tolerances)
 # --------------------------------------------------------------------------------------
 def max_abs(a: np.ndarray, b: np.ndarray) -> float:

@@ -73,3 +73,17 @@ def test_extension_module_exposes_the_reference_entry_points():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     assert hasattr(mod, "dual_mxfp8_head64_sparse_prefill_fwd") and hasattr(mod, "dual_mxfp8_sparse_decode_fwd")
+
+
+def test_topk_argument_checks_need_no_gpu():
+    from mxdsa_b200 import capi
+    L = capi.lib()
+    assert L.mxdsa_topk_select(None) == 1
+    ok = dict(scores=16, indices=16, rows=4, group=1, s_kv=16, topk=4)
+    assert L.mxdsa_topk_select(ctypes.byref(capi.TopkParams(**{**ok, "scores": None}))) == 1
+    assert L.mxdsa_topk_select(ctypes.byref(capi.TopkParams(**{**ok, "s_kv": 10}))) == 2     # not a multiple of 4
+    assert L.mxdsa_topk_select(ctypes.byref(capi.TopkParams(**{**ok, "group": 3}))) == 2
+    assert L.mxdsa_topk_select(ctypes.byref(capi.TopkParams(**{**ok, "topk": 0}))) == 2
+    assert L.mxdsa_topk_select(ctypes.byref(capi.TopkParams(**{**ok, "scores": 20}))) == 3   # scores not 16-byte aligned
+    assert L.mxdsa_topk_select(ctypes.byref(capi.TopkParams(**{**ok, "score_stride": 12}))) == 3   # stride below s_kv
+    assert L.mxdsa_topk_select(ctypes.byref(capi.TopkParams(**{**ok, "rows": 0}))) == 0
