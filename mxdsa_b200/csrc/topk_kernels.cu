@@ -35,6 +35,7 @@ constexpr int kChunks = 8;                         // float4 loads per thread an
 constexpr int kKpt = kChunks * 4;                  // keys per thread and sweep
 constexpr int kSweep = kThreads * kKpt;            // 16 384 keys
 constexpr int kBins = 2048;
+constexpr int kCandCap = 256;                      // candidates kept per warp (of its 1024 keys)
 
 struct TopkShared {
     uint32_t hist[kBins];
@@ -42,15 +43,16 @@ struct TopkShared {
     uint32_t chunk_tot[kChunks * kWarps];          // output scan: packed (greater | equal << 16) per (chunk, warp)
     uint32_t sel_bin, sel_above, sel_count;        // result of find_bin
     uint32_t sweep_tot;                            // packed totals of one sweep
+    uint32_t overflow;                             // a warp's candidate list did not fit: passes 1-2 read the registers
+    uint32_t cand[kWarps][kCandCap];               // per warp: its keys that fall into the threshold bin of pass 0
 };
 
-// float -> unsigned key with the same order; 0 = not a candidate
+// float -> unsigned key with the same order; 0 = not a candidate.  Usable scores map to
+// [0x00800000 (-FLT_MAX), 0xff800000 (+inf)]; -inf and every NaN fall outside that interval.
 __device__ __forceinline__ uint32_t score_key(float s, bool in_range) {
-    s = s + 0.0f;                                  // -0 -> +0
-    const uint32_t u = __float_as_uint(s);
-    const uint32_t k = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-    const bool usable = in_range && (u & 0x7fffffffu) <= 0x7f800000u && u != 0xff800000u;   // no NaN, no -inf
-    return usable ? k : 0u;
+    const uint32_t u = __float_as_uint(s + 0.0f);                                 // -0 -> +0
+    const uint32_t k = u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u);
+    return (in_range && (k - 0x00800000u) <= 0xff000000u) ? k : 0u;
 }
 
 // One sweep of a row into registers.  All loads of a batch are issued before the first conversion, so a
@@ -78,10 +80,11 @@ __device__ __forceinline__ void load_keys(const float* __restrict__ row0, const 
             const int j = sweep * kSweep + ((c0 + c) * kThreads + (int)threadIdx.x) * 4;
             float4 v = a[c];
             if (GROUP == 2) v = make_float4(fmaxf(v.x, b[c].x), fmaxf(v.y, b[c].y), fmaxf(v.z, b[c].z), fmaxf(v.w, b[c].w));
-            key[4 * (c0 + c) + 0] = score_key(v.x, j + 0 < len);
-            key[4 * (c0 + c) + 1] = score_key(v.y, j + 1 < len);
-            key[4 * (c0 + c) + 2] = score_key(v.z, j + 2 < len);
-            key[4 * (c0 + c) + 3] = score_key(v.w, j + 3 < len);
+            const int nin = len - j;                  // keys of this chunk inside the row's length
+            key[4 * (c0 + c) + 0] = score_key(v.x, nin > 0);
+            key[4 * (c0 + c) + 1] = score_key(v.y, nin > 1);
+            key[4 * (c0 + c) + 2] = score_key(v.z, nin > 2);
+            key[4 * (c0 + c) + 3] = score_key(v.w, nin > 3);
         }
     }
 }
@@ -100,7 +103,8 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, int lane) {
 // Ends with a barrier; the result is in sm.sel_*.
 __device__ __forceinline__ uint32_t find_bin(TopkShared& sm, uint32_t k_or_cap, bool cap_to_total, uint32_t& k_out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint4 h = *reinterpret_cast<const uint4*>(&sm.hist[4 * tid]);
+    uint4 h = *reinterpret_cast<const uint4*>(&sm.hist[4 * tid]);
+    if (cap_to_total && tid == 0) h = make_uint4(0u, 0u, 0u, 0u);   // pass 0: bin 0 collects the non-candidates
     const uint32_t local = h.x + h.y + h.z + h.w;
     const uint32_t inc = warp_inclusive_scan(local, lane);
     if (lane == 31) sm.warp_tot[warp] = inc;
@@ -129,6 +133,77 @@ __device__ __forceinline__ uint32_t find_bin(TopkShared& sm, uint32_t k_or_cap, 
     return total;
 }
 
+// Writes the selected keys of one sweep at their output positions and advances the running counts.
+// Per thread and chunk the counts (0..4) are packed four chunks to a word, 8 bits each, so two warp scans
+// cover the eight chunks (a warp's inclusive total per chunk is at most 128).
+template <bool TIES>
+__device__ __forceinline__ void emit_sweep(TopkShared& sm, const uint32_t (&key)[kKpt], uint32_t thr, uint32_t need_eq,
+                                           int32_t* __restrict__ out, int32_t off, int sw, uint32_t& base_gt,
+                                           uint32_t& base_eq) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t own_a[2] = {0u, 0u}, own_e[2] = {0u, 0u};   // a: key > thr (TIES) or key >= thr; e: key == thr
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        uint32_t na = 0, ne = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t kk = key[4 * c + e];
+            na += (TIES ? kk > thr : kk >= thr) ? 1u : 0u;
+            if (TIES) ne += kk == thr ? 1u : 0u;
+        }
+        own_a[c >> 2] |= na << (8 * (c & 3));
+        if (TIES) own_e[c >> 2] |= ne << (8 * (c & 3));
+    }
+    uint32_t inc_a[2], inc_e[2] = {0u, 0u};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        inc_a[h] = warp_inclusive_scan(own_a[h], lane);
+        if (TIES) inc_e[h] = warp_inclusive_scan(own_e[h], lane);
+    }
+    if (lane == 31) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+            sm.chunk_tot[c * kWarps + warp] = ((inc_a[c >> 2] >> (8 * (c & 3))) & 0xffu) | (((inc_e[c >> 2] >> (8 * (c & 3))) & 0xffu) << 16);
+    }
+    __syncthreads();
+    if (warp == 0) {                     // exclusive scan of the 128 (chunk, warp) totals, packed a | e << 16
+        const uint4 t = *reinterpret_cast<const uint4*>(&sm.chunk_tot[4 * lane]);
+        const uint32_t s = t.x + t.y + t.z + t.w;
+        const uint32_t incl = warp_inclusive_scan(s, lane);
+        const uint32_t ex = incl - s;
+        *reinterpret_cast<uint4*>(&sm.chunk_tot[4 * lane]) = make_uint4(ex, ex + t.x, ex + t.x + t.y, ex + t.x + t.y + t.z);
+        if (lane == 31) sm.sweep_tot = incl;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const uint32_t before = sm.chunk_tot[c * kWarps + warp];
+        const int sh = 8 * (c & 3);
+        uint32_t a = base_gt + (before & 0xffffu) + ((inc_a[c >> 2] >> sh) & 0xffu) - ((own_a[c >> 2] >> sh) & 0xffu);
+        const int j0 = sw * kSweep + (c * kThreads + tid) * 4 + off;
+        if (!TIES) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (key[4 * c + e] >= thr) out[a++] = j0 + e;
+            }
+        } else {
+            uint32_t q = base_eq + (before >> 16) + ((inc_e[c >> 2] >> sh) & 0xffu) - ((own_e[c >> 2] >> sh) & 0xffu);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t kk = key[4 * c + e];
+                const bool is_gt = kk > thr, is_eq = kk == thr;
+                if (is_gt || (is_eq && q < need_eq)) out[a + min(q, need_eq)] = j0 + e;
+                a += is_gt ? 1u : 0u;
+                q += is_eq ? 1u : 0u;
+            }
+        }
+    }
+    const uint32_t st = sm.sweep_tot;
+    base_gt += st & 0xffffu;
+    base_eq += st >> 16;
+    __syncthreads();                     // chunk_tot / sweep_tot are rewritten by the next sweep or row
+}
+
 template <int GROUP>
 __global__ void __launch_bounds__(kThreads, 2)
 mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride, const int32_t* __restrict__ lengths,
@@ -145,21 +220,38 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
         uint32_t key[kKpt];
 
         // ---- three radix passes: prefix = the bits of the threshold key found so far
-        uint32_t prefix = 0, k = (uint32_t)topk, n_sel = 0;
+        uint32_t prefix = 0, k = (uint32_t)topk, n_sel = 0, n_cand = 0;
+        const bool use_lists = nsweeps == 1;         // the row sits in registers: passes 1-2 can run on compacted lists
 #pragma unroll 1
         for (int pass = 0; pass < 3; ++pass) {
             const int lo = pass == 0 ? 21 : (pass == 1 ? 10 : 0);       // lowest bit of this pass's digit
             const int hi = pass == 0 ? 32 : (pass == 1 ? 21 : 10);      // bits above the digit are the prefix
             const uint32_t mask = pass == 2 ? 0x3ffu : 0x7ffu;
             *reinterpret_cast<uint4*>(&sm.hist[4 * tid]) = make_uint4(0u, 0u, 0u, 0u);
+            if (pass == 0 && tid == 0) sm.overflow = 0u;
             __syncthreads();
+            if (pass == 0) {
+                // every key takes part (non-candidates are key 0 -> bin 0, which find_bin ignores)
 #pragma unroll 1
-            for (int sw = 0; sw < nsweeps; ++sw) {
-                if (pass == 0 || nsweeps > 1) load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
+                for (int sw = 0; sw < nsweeps; ++sw) {
+                    load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
 #pragma unroll
-                for (int i = 0; i < kKpt; ++i) {
-                    const bool in = pass == 0 ? key[i] != 0u : (key[i] >> hi) == prefix;
-                    if (in) atomicAdd(&sm.hist[(key[i] >> lo) & mask], 1u);
+                    for (int i = 0; i < kKpt; ++i) atomicAdd(&sm.hist[key[i] >> 21], 1u);
+                }
+            } else if (use_lists && sm.overflow == 0u) {
+                // the few keys of the threshold bin, from this warp's list
+                for (uint32_t t = lane; t < n_cand; t += 32) {
+                    const uint32_t kk = sm.cand[warp][t];
+                    if ((kk >> hi) == prefix) atomicAdd(&sm.hist[(kk >> lo) & mask], 1u);
+                }
+            } else {
+#pragma unroll 1
+                for (int sw = 0; sw < nsweeps; ++sw) {
+                    if (nsweeps > 1) load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
+#pragma unroll
+                    for (int i = 0; i < kKpt; ++i) {
+                        if ((key[i] >> hi) == prefix) atomicAdd(&sm.hist[(key[i] >> lo) & mask], 1u);
+                    }
                 }
             }
             __syncthreads();
@@ -169,56 +261,39 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
             if (total == 0u || k_now == 0u) { n_sel = 0; break; }
             prefix = pass == 0 ? sm.sel_bin : ((prefix << (hi - lo)) | sm.sel_bin);
             k = k_now - sm.sel_above;                // rank inside the chosen bin, 1-based
+            if (pass == 0 && use_lists) {
+                // warp-private compaction of the keys in the threshold bin: ballot ranks, no atomics
+                n_cand = 0;
+#pragma unroll
+                for (int i = 0; i < kKpt; ++i) {
+                    const bool in = (key[i] >> 21) == prefix;
+                    const uint32_t b = __ballot_sync(0xffffffffu, in);
+                    if (b != 0u) {
+                        const uint32_t at = n_cand + __popc(b & ((1u << lane) - 1u));
+                        if (in && at < (uint32_t)kCandCap) sm.cand[warp][at] = key[i];
+                        n_cand += __popc(b);
+                    }
+                }
+                if (n_cand > (uint32_t)kCandCap && lane == 0) sm.overflow = 1u;
+                __syncwarp();
+            }
         }
         // all threads agree on n_sel (computed from shared totals); prefix is now the full threshold key
         const uint32_t thr = prefix, need_eq = k;    // take `need_eq` keys equal to thr, smallest index first
 
-        // ---- output positions: ascending index, order (sweep, chunk, thread, element)
+        // ---- output positions: ascending index, order (sweep, chunk, thread, element).
+        // Without surplus ties (every key equal to the threshold is taken -- the rule unless scores repeat)
+        // "selected" is key >= thr and one count per key suffices; otherwise the equal keys are ranked too.
         int32_t* out = indices + (long long)r * index_stride;
         const int32_t off = row_offset != nullptr ? __ldg(row_offset + r) : 0;
         if (n_sel > 0u) {
+            const bool ties = need_eq != sm.sel_count;
             uint32_t base_gt = 0, base_eq = 0;
 #pragma unroll 1
             for (int sw = 0; sw < nsweeps; ++sw) {
                 if (nsweeps > 1) load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
-                uint32_t inc[kChunks], own[kChunks];
-#pragma unroll
-                for (int c = 0; c < kChunks; ++c) {
-                    uint32_t v = 0;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) v += (key[4 * c + e] > thr ? 1u : 0u) + (key[4 * c + e] == thr ? 0x10000u : 0u);
-                    own[c] = v;
-                    inc[c] = warp_inclusive_scan(v, lane);
-                    if (lane == 31) sm.chunk_tot[c * kWarps + warp] = inc[c];
-                }
-                __syncthreads();
-                if (warp == 0) {                     // exclusive scan of the 128 (chunk, warp) totals
-                    const uint4 t = *reinterpret_cast<const uint4*>(&sm.chunk_tot[4 * lane]);
-                    const uint32_t s = t.x + t.y + t.z + t.w;
-                    const uint32_t incl = warp_inclusive_scan(s, lane);
-                    const uint32_t ex = incl - s;
-                    *reinterpret_cast<uint4*>(&sm.chunk_tot[4 * lane]) = make_uint4(ex, ex + t.x, ex + t.x + t.y, ex + t.x + t.y + t.z);
-                    if (lane == 31) sm.sweep_tot = incl;
-                }
-                __syncthreads();
-#pragma unroll
-                for (int c = 0; c < kChunks; ++c) {
-                    const uint32_t before = sm.chunk_tot[c * kWarps + warp] + inc[c] - own[c];
-                    uint32_t gt = base_gt + (before & 0xffffu), eq = base_eq + (before >> 16);
-                    const int j0 = sw * kSweep + (c * kThreads + tid) * 4;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t kk = key[4 * c + e];
-                        const bool is_gt = kk > thr, is_eq = kk == thr;
-                        if (is_gt || (is_eq && eq < need_eq)) out[gt + min(eq, need_eq)] = j0 + e + off;
-                        gt += is_gt ? 1u : 0u;
-                        eq += is_eq ? 1u : 0u;
-                    }
-                }
-                const uint32_t st = sm.sweep_tot;
-                base_gt += st & 0xffffu;
-                base_eq += st >> 16;
-                __syncthreads();                     // chunk_tot / sweep_tot are rewritten by the next sweep or row
+                if (!ties) emit_sweep<false>(sm, key, thr, need_eq, out, off, sw, base_gt, base_eq);
+                else emit_sweep<true>(sm, key, thr, need_eq, out, off, sw, base_gt, base_eq);
             }
         }
         for (uint32_t pos = n_sel + tid; pos < (uint32_t)topk; pos += kThreads) out[pos] = -1;
