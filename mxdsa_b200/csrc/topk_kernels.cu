@@ -35,16 +35,15 @@ constexpr int kChunks = 8;                         // float4 loads per thread an
 constexpr int kKpt = kChunks * 4;                  // keys per thread and sweep
 constexpr int kSweep = kThreads * kKpt;            // 16 384 keys
 constexpr int kBins = 2048;
-constexpr int kCandCap = 256;                      // candidates kept per warp (of its 1024 keys)
+constexpr int kStage = 4096;                       // rows of up to this many indices are staged in shared memory
 
 struct TopkShared {
-    uint32_t hist[kBins];
+    uint32_t hist[kBins + 32];                     // + one never-read bin per lane for keys outside the current prefix
     uint32_t warp_tot[kWarps];                     // find_bin: per-warp histogram mass
     uint32_t chunk_tot[kChunks * kWarps];          // output scan: packed (greater | equal << 16) per (chunk, warp)
     uint32_t sel_bin, sel_above, sel_count;        // result of find_bin
     uint32_t sweep_tot;                            // packed totals of one sweep
-    uint32_t overflow;                             // a warp's candidate list did not fit: passes 1-2 read the registers
-    uint32_t cand[kWarps][kCandCap];               // per warp: its keys that fall into the threshold bin of pass 0
+    int32_t stage[kStage];                         // a row's output, staged for coalesced stores
 };
 
 // float -> unsigned key with the same order; 0 = not a candidate.  Usable scores map to
@@ -210,7 +209,7 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
                        const int32_t* __restrict__ row_offset, int32_t* __restrict__ indices, long long index_stride,
                        int32_t* __restrict__ topk_length, int rows, int s_kv, int topk) {
     __shared__ __align__(16) TopkShared sm;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
     const int nsweeps = (s_kv + kSweep - 1) / kSweep;
     for (int r = blockIdx.x; r < rows; r += gridDim.x) {
         const float* row0 = scores + (long long)r * GROUP * score_stride;
@@ -218,17 +217,21 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
         int len = s_kv;
         if (lengths != nullptr) len = min(max(__ldg(lengths + r), 0), s_kv);
         uint32_t key[kKpt];
+        // the row this CTA takes next: ask L2 for it now, so that its loads do not wait for HBM
+        if (r + (int)gridDim.x < rows && tid * 32 < s_kv && nsweeps == 1) {
+            const float* nx = scores + (long long)(r + (int)gridDim.x) * GROUP * score_stride + tid * 32;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nx));
+            if (GROUP == 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + score_stride));
+        }
 
         // ---- three radix passes: prefix = the bits of the threshold key found so far
-        uint32_t prefix = 0, k = (uint32_t)topk, n_sel = 0, n_cand = 0;
-        const bool use_lists = nsweeps == 1;         // the row sits in registers: passes 1-2 can run on compacted lists
+        uint32_t prefix = 0, k = (uint32_t)topk, n_sel = 0;
 #pragma unroll 1
         for (int pass = 0; pass < 3; ++pass) {
             const int lo = pass == 0 ? 21 : (pass == 1 ? 10 : 0);       // lowest bit of this pass's digit
             const int hi = pass == 0 ? 32 : (pass == 1 ? 21 : 10);      // bits above the digit are the prefix
             const uint32_t mask = pass == 2 ? 0x3ffu : 0x7ffu;
             *reinterpret_cast<uint4*>(&sm.hist[4 * tid]) = make_uint4(0u, 0u, 0u, 0u);
-            if (pass == 0 && tid == 0) sm.overflow = 0u;
             __syncthreads();
             if (pass == 0) {
                 // every key takes part (non-candidates are key 0 -> bin 0, which find_bin ignores)
@@ -238,19 +241,15 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
 #pragma unroll
                     for (int i = 0; i < kKpt; ++i) atomicAdd(&sm.hist[key[i] >> 21], 1u);
                 }
-            } else if (use_lists && sm.overflow == 0u) {
-                // the few keys of the threshold bin, from this warp's list
-                for (uint32_t t = lane; t < n_cand; t += 32) {
-                    const uint32_t kk = sm.cand[warp][t];
-                    if ((kk >> hi) == prefix) atomicAdd(&sm.hist[(kk >> lo) & mask], 1u);
-                }
             } else {
+                // keys outside the prefix add to a per-lane spare bin: no branch, no bank conflict
 #pragma unroll 1
                 for (int sw = 0; sw < nsweeps; ++sw) {
                     if (nsweeps > 1) load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
 #pragma unroll
                     for (int i = 0; i < kKpt; ++i) {
-                        if ((key[i] >> hi) == prefix) atomicAdd(&sm.hist[(key[i] >> lo) & mask], 1u);
+                        const uint32_t bin = (key[i] >> hi) == prefix ? ((key[i] >> lo) & mask) : (uint32_t)(kBins + lane);
+                        atomicAdd(&sm.hist[bin], 1u);
                     }
                 }
             }
@@ -261,22 +260,6 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
             if (total == 0u || k_now == 0u) { n_sel = 0; break; }
             prefix = pass == 0 ? sm.sel_bin : ((prefix << (hi - lo)) | sm.sel_bin);
             k = k_now - sm.sel_above;                // rank inside the chosen bin, 1-based
-            if (pass == 0 && use_lists) {
-                // warp-private compaction of the keys in the threshold bin: ballot ranks, no atomics
-                n_cand = 0;
-#pragma unroll
-                for (int i = 0; i < kKpt; ++i) {
-                    const bool in = (key[i] >> 21) == prefix;
-                    const uint32_t b = __ballot_sync(0xffffffffu, in);
-                    if (b != 0u) {
-                        const uint32_t at = n_cand + __popc(b & ((1u << lane) - 1u));
-                        if (in && at < (uint32_t)kCandCap) sm.cand[warp][at] = key[i];
-                        n_cand += __popc(b);
-                    }
-                }
-                if (n_cand > (uint32_t)kCandCap && lane == 0) sm.overflow = 1u;
-                __syncwarp();
-            }
         }
         // all threads agree on n_sel (computed from shared totals); prefix is now the full threshold key
         const uint32_t thr = prefix, need_eq = k;    // take `need_eq` keys equal to thr, smallest index first
@@ -286,17 +269,23 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
         // "selected" is key >= thr and one count per key suffices; otherwise the equal keys are ranked too.
         int32_t* out = indices + (long long)r * index_stride;
         const int32_t off = row_offset != nullptr ? __ldg(row_offset + r) : 0;
+        const bool staged = topk <= kStage;          // positions go to shared memory first, then out in whole lines
+        int32_t* dst = staged ? sm.stage : out;
         if (n_sel > 0u) {
             const bool ties = need_eq != sm.sel_count;
             uint32_t base_gt = 0, base_eq = 0;
 #pragma unroll 1
             for (int sw = 0; sw < nsweeps; ++sw) {
                 if (nsweeps > 1) load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
-                if (!ties) emit_sweep<false>(sm, key, thr, need_eq, out, off, sw, base_gt, base_eq);
-                else emit_sweep<true>(sm, key, thr, need_eq, out, off, sw, base_gt, base_eq);
+                if (!ties) emit_sweep<false>(sm, key, thr, need_eq, dst, off, sw, base_gt, base_eq);
+                else emit_sweep<true>(sm, key, thr, need_eq, dst, off, sw, base_gt, base_eq);
             }
         }
-        for (uint32_t pos = n_sel + tid; pos < (uint32_t)topk; pos += kThreads) out[pos] = -1;
+        if (staged) {
+            for (uint32_t pos = tid; pos < (uint32_t)topk; pos += kThreads) out[pos] = pos < n_sel ? sm.stage[pos] : -1;
+        } else {
+            for (uint32_t pos = n_sel + tid; pos < (uint32_t)topk; pos += kThreads) out[pos] = -1;
+        }
         if (topk_length != nullptr && tid == 0) topk_length[r] = (int32_t)n_sel;
         __syncthreads();                             // sm.sel_* and the histogram belong to the next row from here
     }
