@@ -46,12 +46,14 @@ struct TopkShared {
     int32_t stage[kStage];                         // a row's output, staged for coalesced stores
 };
 
-// float -> unsigned key with the same order; 0 = not a candidate.  Usable scores map to
-// [0x00800000 (-FLT_MAX), 0xff800000 (+inf)]; -inf and every NaN fall outside that interval.
+// float -> unsigned key with the same order.  Usable scores map to [0x00800000 (-FLT_MAX), 0xff800000
+// (+inf)].  -inf and the negative NaNs land below that interval: they fall into histogram bins 0-3, which
+// pass 0 ignores, and lie below every threshold, so they need no special case.  Positive NaNs (above the
+// interval) and keys outside the row's length become 0.
 __device__ __forceinline__ uint32_t score_key(float s, bool in_range) {
     const uint32_t u = __float_as_uint(s + 0.0f);                                 // -0 -> +0
     const uint32_t k = u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u);
-    return (in_range && (k - 0x00800000u) <= 0xff000000u) ? k : 0u;
+    return (in_range && k <= 0xff800000u) ? k : 0u;
 }
 
 // One sweep of a row into registers.  All loads of a batch are issued before the first conversion, so a
@@ -80,10 +82,17 @@ __device__ __forceinline__ void load_keys(const float* __restrict__ row0, const 
             float4 v = a[c];
             if (GROUP == 2) v = make_float4(fmaxf(v.x, b[c].x), fmaxf(v.y, b[c].y), fmaxf(v.z, b[c].z), fmaxf(v.w, b[c].w));
             const int nin = len - j;                  // keys of this chunk inside the row's length
-            key[4 * (c0 + c) + 0] = score_key(v.x, nin > 0);
-            key[4 * (c0 + c) + 1] = score_key(v.y, nin > 1);
-            key[4 * (c0 + c) + 2] = score_key(v.z, nin > 2);
-            key[4 * (c0 + c) + 3] = score_key(v.w, nin > 3);
+            if (nin >= 4) {
+                key[4 * (c0 + c) + 0] = score_key(v.x, true);
+                key[4 * (c0 + c) + 1] = score_key(v.y, true);
+                key[4 * (c0 + c) + 2] = score_key(v.z, true);
+                key[4 * (c0 + c) + 3] = score_key(v.w, true);
+            } else {
+                key[4 * (c0 + c) + 0] = score_key(v.x, nin > 0);
+                key[4 * (c0 + c) + 1] = score_key(v.y, nin > 1);
+                key[4 * (c0 + c) + 2] = score_key(v.z, nin > 2);
+                key[4 * (c0 + c) + 3] = score_key(v.w, nin > 3);
+            }
         }
     }
 }
@@ -100,10 +109,11 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, int lane) {
 // After a histogram is complete: the bin that holds the k-th largest entry (k counted from the top,
 // 1 <= k <= total), the mass above that bin and the bin's own count.  Returns the histogram total.
 // Ends with a barrier; the result is in sm.sel_*.
-__device__ __forceinline__ uint32_t find_bin(TopkShared& sm, uint32_t k_or_cap, bool cap_to_total, uint32_t& k_out) {
+__device__ __forceinline__ uint32_t find_bin(TopkShared& sm, uint32_t k_or_cap, bool cap_to_total, uint32_t& k_out, int nbins) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint4 h = *reinterpret_cast<const uint4*>(&sm.hist[4 * tid]);
-    if (cap_to_total && tid == 0) h = make_uint4(0u, 0u, 0u, 0u);   // pass 0: bin 0 collects the non-candidates
+    if (cap_to_total && tid == 0) h = make_uint4(0u, 0u, 0u, 0u);   // pass 0: bins 0-3 collect the non-candidates
+    if (4 * tid >= nbins) h = make_uint4(0u, 0u, 0u, 0u);           // beyond the digits: spare bins
     const uint32_t local = h.x + h.y + h.z + h.w;
     const uint32_t inc = warp_inclusive_scan(local, lane);
     if (lane == 31) sm.warp_tot[warp] = inc;
@@ -230,7 +240,6 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
         for (int pass = 0; pass < 3; ++pass) {
             const int lo = pass == 0 ? 21 : (pass == 1 ? 10 : 0);       // lowest bit of this pass's digit
             const int hi = pass == 0 ? 32 : (pass == 1 ? 21 : 10);      // bits above the digit are the prefix
-            const uint32_t mask = pass == 2 ? 0x3ffu : 0x7ffu;
             *reinterpret_cast<uint4*>(&sm.hist[4 * tid]) = make_uint4(0u, 0u, 0u, 0u);
             __syncthreads();
             if (pass == 0) {
@@ -246,16 +255,16 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
 #pragma unroll 1
                 for (int sw = 0; sw < nsweeps; ++sw) {
                     if (nsweeps > 1) load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
+                    // distance from the first key of the prefix: inside the prefix it is below 2^hi and its top
+                    // bits are the digit; everything else (wrapped or large) is clamped onto the spare bins
+                    const uint32_t first = prefix << hi, spare = (uint32_t)((kBins >> (pass - 1)) + lane);   // 2048 / 1024 digits
 #pragma unroll
-                    for (int i = 0; i < kKpt; ++i) {
-                        const uint32_t bin = (key[i] >> hi) == prefix ? ((key[i] >> lo) & mask) : (uint32_t)(kBins + lane);
-                        atomicAdd(&sm.hist[bin], 1u);
-                    }
+                    for (int i = 0; i < kKpt; ++i) atomicAdd(&sm.hist[min((key[i] - first) >> lo, spare)], 1u);
                 }
             }
             __syncthreads();
             uint32_t k_now;
-            const uint32_t total = find_bin(sm, k, pass == 0, k_now);
+            const uint32_t total = find_bin(sm, k, pass == 0, k_now, pass == 2 ? kBins / 2 : kBins);
             if (pass == 0) n_sel = k_now;            // min(topk, candidates)
             if (total == 0u || k_now == 0u) { n_sel = 0; break; }
             prefix = pass == 0 ? sm.sel_bin : ((prefix << (hi - lo)) | sm.sel_bin);
