@@ -118,25 +118,24 @@ __device__ __forceinline__ uint32_t find_bin(TopkShared& sm, uint32_t k_or_cap, 
     const uint32_t inc = warp_inclusive_scan(local, lane);
     if (lane == 31) sm.warp_tot[warp] = inc;
     __syncthreads();
-    uint32_t below_warps = 0, total = 0;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        const uint32_t t = sm.warp_tot[w];
-        below_warps += w < warp ? t : 0u;
-        total += t;
-    }
+    // lane l holds warp l's mass; two warp reductions give the total and the mass of the warps below
+    const uint32_t wt = lane < kWarps ? sm.warp_tot[lane] : 0u;
+    const uint32_t total = __reduce_add_sync(0xffffffffu, wt);
+    const uint32_t below_warps = __reduce_add_sync(0xffffffffu, lane < warp ? wt : 0u);
     const uint32_t k = cap_to_total ? min(k_or_cap, total) : k_or_cap;
     k_out = k;
     uint32_t run = total - (below_warps + inc);    // mass in bins above this thread's four
-    const uint32_t hh[4] = {h.x, h.y, h.z, h.w};
+    if (run < k && run + local >= k) {             // the k-th entry is in one of this thread's bins
+        const uint32_t hh[4] = {h.x, h.y, h.z, h.w};
 #pragma unroll
-    for (int b = 3; b >= 0; --b) {
-        if (run < k && run + hh[b] >= k) {
-            sm.sel_bin = 4 * tid + b;
-            sm.sel_above = run;
-            sm.sel_count = hh[b];
+        for (int b = 3; b >= 0; --b) {
+            if (run < k && run + hh[b] >= k) {
+                sm.sel_bin = 4 * tid + b;
+                sm.sel_above = run;
+                sm.sel_count = hh[b];
+            }
+            run += hh[b];
         }
-        run += hh[b];
     }
     __syncthreads();
     return total;
