@@ -23,6 +23,7 @@
 //
 // Bound: HBM.  Algorithmic bytes per row: group * s_kv * 4 read + topk * 4 written.
 #include <cuda_runtime.h>
+#include <math_constants.h>
 #include <stdint.h>
 
 #include "../../include/mxdsa.h"
@@ -47,13 +48,12 @@ struct TopkShared {
 };
 
 // float -> unsigned key with the same order.  Usable scores map to [0x00800000 (-FLT_MAX), 0xff800000
-// (+inf)].  -inf and the negative NaNs land below that interval: they fall into histogram bins 0-3, which
-// pass 0 ignores, and lie below every threshold, so they need no special case.  Positive NaNs (above the
-// interval) and keys outside the row's length become 0.
-__device__ __forceinline__ uint32_t score_key(float s, bool in_range) {
-    const uint32_t u = __float_as_uint(s + 0.0f);                                 // -0 -> +0
-    const uint32_t k = u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u);
-    return (in_range && k <= 0xff800000u) ? k : 0u;
+// (+inf)].  A NaN is first turned into -inf (fmaxf returns its other argument); -inf lands just below the
+// usable interval: it falls into histogram bins 0-3, which pass 0 ignores, and lies below every threshold,
+// so it needs no further special case.  Keys outside the row's length become 0.
+__device__ __forceinline__ uint32_t score_key(float s) {
+    const uint32_t u = __float_as_uint(fmaxf(s, -CUDART_INF_F) + 0.0f);           // NaN -> -inf, -0 -> +0
+    return u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u);
 }
 
 // One sweep of a row into registers.  All loads of a batch are issued before the first conversion, so a
@@ -82,16 +82,13 @@ __device__ __forceinline__ void load_keys(const float* __restrict__ row0, const 
             float4 v = a[c];
             if (GROUP == 2) v = make_float4(fmaxf(v.x, b[c].x), fmaxf(v.y, b[c].y), fmaxf(v.z, b[c].z), fmaxf(v.w, b[c].w));
             const int nin = len - j;                  // keys of this chunk inside the row's length
-            if (nin >= 4) {
-                key[4 * (c0 + c) + 0] = score_key(v.x, true);
-                key[4 * (c0 + c) + 1] = score_key(v.y, true);
-                key[4 * (c0 + c) + 2] = score_key(v.z, true);
-                key[4 * (c0 + c) + 3] = score_key(v.w, true);
-            } else {
-                key[4 * (c0 + c) + 0] = score_key(v.x, nin > 0);
-                key[4 * (c0 + c) + 1] = score_key(v.y, nin > 1);
-                key[4 * (c0 + c) + 2] = score_key(v.z, nin > 2);
-                key[4 * (c0 + c) + 3] = score_key(v.w, nin > 3);
+            key[4 * (c0 + c) + 0] = score_key(v.x);
+            key[4 * (c0 + c) + 1] = score_key(v.y);
+            key[4 * (c0 + c) + 2] = score_key(v.z);
+            key[4 * (c0 + c) + 3] = score_key(v.w);
+            if (nin < 4) {                            // the chunk straddles (or lies beyond) the row's length
+#pragma unroll
+                for (int e = 0; e < 4; ++e) key[4 * (c0 + c) + e] = e < nin ? key[4 * (c0 + c) + e] : 0u;
             }
         }
     }
