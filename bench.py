@@ -307,7 +307,9 @@ def topk_headline(torch, peaks, steps, warmup):
     gbs = alg_bytes / ms / 1e6
     return dict(pairs=pairs, s_kv=s_kv, topk=topk, ms=ms, torch_chain_ms=ms_chain, algorithmic_bytes=alg_bytes,
                 roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
-                              frac=gbs / peaks["hbm_gbs"], traffic=None))
+                              frac=gbs / peaks["hbm_gbs"],
+                              # DRAM bytes of one launch: 362 MB captured for 2048 pairs, scaled by the pairs
+                              traffic=362e6 * pairs / 2048, traffic_unit="bytes per launch"))
 
 
 def reference_gpu(torch, q, kv, idx, w1, w2, steps, warmup):
