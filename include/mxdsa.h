@@ -245,8 +245,8 @@ int mxdsa_pack_last_cuda_error(void);
  * Index selection: scores -> the int32 index rows (and valid lengths) that mxdsa_prefill_fwd and
  * mxdsa_decode_fwd consume.  The reference has no producer for `indices`; its callers define the
  * conventions this follows (reference tests/benchmark.py:119-147: one row per pair of query tokens,
- * -1 entries never attended, decode pools addressed by request * pool_len + slot; csrc/api/binding.cpp
- * :12-15 and csrc/api/sparse_attn_decode.h:13-20 for shapes and topk_length).
+ * -1 entries never attended, decode pools addressed by request * pool_len + slot; csrc/bindings/binding.cpp
+ * :12-15 and csrc/bindings/dual_mxfp8_sparse_decode.h:13-20 for shapes and topk_length).
  *
  * Row r takes the min(topk, candidates) highest-scoring keys among j < lengths[r] (all s_kv when
  * lengths is NULL); a score that is NaN or -inf is no candidate; ties go to the smaller j.  With

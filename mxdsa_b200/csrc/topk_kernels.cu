@@ -3,8 +3,8 @@
 //
 // The attention operators take their keys from `indices[pair][topk]` with the conventions of the
 // reference's callers (reference tests/benchmark.py:119-147: one row per pair of query tokens, entries
-// -1 never attended, decode pools addressed by request * pool_len + slot; binding.cpp:12-15 and
-// sparse_attn_decode.h:13-20 for the shapes; `topk_length` bounds the attended prefix).  The reference
+// -1 never attended, decode pools addressed by request * pool_len + slot; csrc/bindings/binding.cpp:12-15 and
+// csrc/bindings/dual_mxfp8_sparse_decode.h:13-20 for the shapes; `topk_length` bounds the attended prefix).  The reference
 // has no producer for that tensor; this is the selection step of a sparse-attention indexer in the
 // form those conventions need.
 //
@@ -17,11 +17,15 @@
 //   * written in ascending j (+ row_offset[r]), then -1 up to topk; topk_length[r] = number selected.
 //
 // Method: exact radix selection on the order-preserving 32-bit image of the float, three histogram
-// passes (11 + 11 + 10 bits) in shared memory, keys of a row held in registers (one HBM read per
-// score for rows of up to 16 384 keys; longer rows are swept again from L2), then two packed block
-// scans give every selected key its output position.  No sort, no global atomics, deterministic.
+// passes (11 + 11 + 10 bits) with shared-memory atomics, keys of a row held in registers (one HBM read
+// per score for rows of up to 16 384 keys; longer rows are swept again from L2).  No pass branches per
+// key: the first counts every key, the later ones send keys outside the current prefix to a per-lane
+// spare bin.  Packed per-chunk counts and two block scans then give every selected key its output
+// position; the row is staged in shared memory and written in whole lines.  No sort, no global atomics,
+// deterministic.
 //
-// Bound: HBM.  Algorithmic bytes per row: group * s_kv * 4 read + topk * 4 written.
+// Bound: HBM on paper (group * s_kv * 4 bytes read + topk * 4 written per row); in practice the integer
+// pipe (about 25 instructions per key), so every step is written to save instructions, not bytes.
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include <stdint.h>
@@ -239,7 +243,7 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
             *reinterpret_cast<uint4*>(&sm.hist[4 * tid]) = make_uint4(0u, 0u, 0u, 0u);
             __syncthreads();
             if (pass == 0) {
-                // every key takes part (non-candidates are key 0 -> bin 0, which find_bin ignores)
+                // every key takes part (non-candidates fall into bins 0-3, which find_bin ignores)
 #pragma unroll 1
                 for (int sw = 0; sw < nsweeps; ++sw) {
                     load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
