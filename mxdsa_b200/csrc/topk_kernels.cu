@@ -145,7 +145,7 @@ __device__ __forceinline__ uint32_t find_bin(TopkShared& sm, uint32_t k_or_cap, 
 // Writes the selected keys of one sweep at their output positions and advances the running counts.
 // Per thread and chunk the counts (0..4) are packed four chunks to a word, 8 bits each, so two warp scans
 // cover the eight chunks (a warp's inclusive total per chunk is at most 128).
-template <bool TIES>
+template <bool TIES, bool STAGED>
 __device__ __forceinline__ void emit_sweep(TopkShared& sm, const uint32_t (&key)[kKpt], uint32_t thr, uint32_t need_eq,
                                            int32_t* __restrict__ out, int32_t off, int sw, uint32_t& base_gt,
                                            uint32_t& base_eq) {
@@ -193,7 +193,10 @@ __device__ __forceinline__ void emit_sweep(TopkShared& sm, const uint32_t (&key)
         if (!TIES) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                if (key[4 * c + e] >= thr) out[a++] = j0 + e;
+                if (key[4 * c + e] >= thr) {
+                    if (STAGED) sm.stage[a++] = j0 + e;
+                    else out[a++] = j0 + e;
+                }
             }
         } else {
             uint32_t q = base_eq + (before >> 16) + ((inc_e[c >> 2] >> sh) & 0xffu) - ((own_e[c >> 2] >> sh) & 0xffu);
@@ -201,7 +204,10 @@ __device__ __forceinline__ void emit_sweep(TopkShared& sm, const uint32_t (&key)
             for (int e = 0; e < 4; ++e) {
                 const uint32_t kk = key[4 * c + e];
                 const bool is_gt = kk > thr, is_eq = kk == thr;
-                if (is_gt || (is_eq && q < need_eq)) out[a + min(q, need_eq)] = j0 + e;
+                if (is_gt || (is_eq && q < need_eq)) {
+                    if (STAGED) sm.stage[a + min(q, need_eq)] = j0 + e;
+                    else out[a + min(q, need_eq)] = j0 + e;
+                }
                 a += is_gt ? 1u : 0u;
                 q += is_eq ? 1u : 0u;
             }
@@ -213,7 +219,7 @@ __device__ __forceinline__ void emit_sweep(TopkShared& sm, const uint32_t (&key)
     __syncthreads();                     // chunk_tot / sweep_tot are rewritten by the next sweep or row
 }
 
-template <int GROUP>
+template <int GROUP, bool STAGED>
 __global__ void __launch_bounds__(kThreads, 2)
 mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride, const int32_t* __restrict__ lengths,
                        const int32_t* __restrict__ row_offset, int32_t* __restrict__ indices, long long index_stride,
@@ -278,19 +284,17 @@ mxdsa_topk_rows_kernel(const float* __restrict__ scores, long long score_stride,
         // "selected" is key >= thr and one count per key suffices; otherwise the equal keys are ranked too.
         int32_t* out = indices + (long long)r * index_stride;
         const int32_t off = row_offset != nullptr ? __ldg(row_offset + r) : 0;
-        const bool staged = topk <= kStage;          // positions go to shared memory first, then out in whole lines
-        int32_t* dst = staged ? sm.stage : out;
         if (n_sel > 0u) {
             const bool ties = need_eq != sm.sel_count;
             uint32_t base_gt = 0, base_eq = 0;
 #pragma unroll 1
             for (int sw = 0; sw < nsweeps; ++sw) {
                 if (nsweeps > 1) load_keys<GROUP>(row0, row1, sw, s_kv, len, key);
-                if (!ties) emit_sweep<false>(sm, key, thr, need_eq, dst, off, sw, base_gt, base_eq);
-                else emit_sweep<true>(sm, key, thr, need_eq, dst, off, sw, base_gt, base_eq);
+                if (!ties) emit_sweep<false, STAGED>(sm, key, thr, need_eq, out, off, sw, base_gt, base_eq);
+                else emit_sweep<true, STAGED>(sm, key, thr, need_eq, out, off, sw, base_gt, base_eq);
             }
         }
-        if (staged) {
+        if (STAGED) {                                // topk <= kStage: positions were staged in shared memory
             for (uint32_t pos = tid; pos < (uint32_t)topk; pos += kThreads) out[pos] = pos < n_sel ? sm.stage[pos] : -1;
         } else {
             for (uint32_t pos = n_sel + tid; pos < (uint32_t)topk; pos += kThreads) out[pos] = -1;
@@ -316,12 +320,10 @@ extern "C" int mxdsa_topk_select(const mxdsa_topk_params* p) {
         return MXDSA_ERR_CUDA;
     const int grid = p->rows < sms * 2 ? p->rows : sms * 2;      // two resident CTAs of 512 threads per SM
     const cudaStream_t s = static_cast<cudaStream_t>(p->stream);
-    if (p->group == 2)
-        mxdsa_topk_rows_kernel<2><<<grid, kThreads, 0, s>>>(p->scores, ss, p->lengths, p->row_offset, p->indices, is,
-                                                            p->topk_length, p->rows, p->s_kv, p->topk);
-    else
-        mxdsa_topk_rows_kernel<1><<<grid, kThreads, 0, s>>>(p->scores, ss, p->lengths, p->row_offset, p->indices, is,
-                                                            p->topk_length, p->rows, p->s_kv, p->topk);
+    auto kern = p->topk <= kStage ? (p->group == 2 ? mxdsa_topk_rows_kernel<2, true> : mxdsa_topk_rows_kernel<1, true>)
+                                  : (p->group == 2 ? mxdsa_topk_rows_kernel<2, false> : mxdsa_topk_rows_kernel<1, false>);
+    kern<<<grid, kThreads, 0, s>>>(p->scores, ss, p->lengths, p->row_offset, p->indices, is, p->topk_length, p->rows, p->s_kv,
+                                   p->topk);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         tl_topk_cuda_error = (int)e;

@@ -29,7 +29,7 @@ def _check(scores, topk, lengths=None, pair=False, row_offset=None):
     assert np.array_equal(got_i, ref_i)
 
 
-@pytest.mark.parametrize("s_kv,topk", [(16384, 4096), (16384, 128), (1024, 128), (4096, 2048), (8, 64), (16388, 512)])
+@pytest.mark.parametrize("s_kv,topk", [(16384, 4096), (16384, 128), (1024, 128), (4096, 2048), (8, 64), (16388, 512), (16384, 6000), (40000, 9000)])
 def test_normal_scores(s_kv, topk):
     rng = np.random.default_rng(s_kv + topk)
     _check(rng.standard_normal((37, s_kv)).astype(np.float32), topk)
@@ -47,6 +47,7 @@ def test_ties_go_to_the_smaller_index():
     rng = np.random.default_rng(11)
     few = rng.integers(0, 5, size=(9, 16384)).astype(np.float32)          # five distinct values
     _check(few, 4096)
+    _check(few, 5000)                                                      # beyond the staged row size
     _check(np.full((3, 2048), 1.5, np.float32), 512)                       # every key ties
     close = (1.0 + rng.integers(0, 7, size=(5, 8192)) * 2.0 ** -23).astype(np.float32)   # differ in the last bits only
     _check(close, 1000)
