@@ -2,7 +2,7 @@
 # TEST INFRASTRUCTURE ONLY -- never part of the shipped library.
 #
 # Compiles the UNMODIFIED reference (dingirsu/MXDSA) from the sources where they lie
-# (default /root/reference, override with MXDSA_REFERENCE_DIR) into oracle/_ref/mxdsa_ext.so.
+# (location: MXDSA_REFERENCE_DIR, or the default set below) into oracle/_ref/mxdsa_ext.so.
 # Nothing is copied: nvcc/c++ read the reference's csrc/ tree in place and only object files
 # and the final .so are written under oracle/_ref/ (git-ignored).
 #
