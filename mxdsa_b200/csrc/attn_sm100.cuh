@@ -123,11 +123,14 @@ struct AttnParams {
     const int* num_splits;    // [b+1]
     float* o_accum;           // [splits][s_q][64][512]
     float* lse_accum;         // [splits][s_q][64]
+    long long pool_rows, extra_pool_rows;     // decode: keys in each pool (num_blocks * page_size); indices beyond are skipped
     unsigned long long* prof; // profiling builds: [2 CTAs][64] stall cycles of cluster 0, else null
 };
 
 struct TensorMaps {
     CUtensorMap q;        // 5-D {128 B, 64 heads, 4 chunks, tokens, requests}
+    CUtensorMap kv;       // 2-D {512 B, rows}: data rows of the (main) KV store, row pitch 512 B; gather4 source for V
+    CUtensorMap ekv;      // decode: the same over the extra pool
 };
 
 // One unit of work for a CTA pair: a query pair and a range of 64-key blocks of its key list.
@@ -148,10 +151,11 @@ struct __align__(1024) SmemPlan {
     uint8_t k[kKStages][4 * 64 * 128];             // [chunk][key of this CTA][128 B]
     uint8_t v[kVStages][2 * 128 * 128];            // [chunk of this CTA][key][128 B]
     uint8_t s[2][64 * 128];                        // [row][128 keys], 128-byte swizzle
+    __align__(16) uint2 kslot[kKStages][kTileKeys]; // scale bytes 0-7 of every key of the tile, as gathered (K ring)
+    __align__(16) uint16_t kvalid[kKStages][8];     // validity bits of the tile's keys, 16 per entry (K ring)
     __align__(128) uint32_t q_sf[64 * 4];          // scale rows for tcgen05.cp (64 rows x 16 B)
-    __align__(128) uint32_t k_sf[kScStages][64 * 4];
+    __align__(128) uint32_t k_sf[kKStages][64 * 4];   // per K stage: written when the stage has landed, read by that tile's QK
     __align__(128) uint32_t s_sf[2][64 * 4];
-    __align__(128) uint32_t v_sf[2][64 * 4];
     __align__(16) float tok_scale[kScStages][kTileKeys];
     __align__(16) uint32_t valid[kScStages][4];
     float xmax[2][2][128];                         // [group][tile parity][lane]: row max of the lane's 64 keys
@@ -161,9 +165,8 @@ struct __align__(1024) SmemPlan {
     uint64_t bar_q_full;                           // CTA0: Q data + scale rows of both CTAs ready
     uint64_t bar_q_empty;                          // both: every QK of the pair finished (2 arrivals)
     uint64_t bar_k_landed[kKStages];               // local: this CTA's K rows landed (128 arrivals)
-    uint64_t bar_v_landed[kVStages];               // local: this CTA's V rows landed
     uint64_t bar_k_full[kKStages];                 // CTA0: CTA1's K rows landed
-    uint64_t bar_v_full[kVStages];                 // CTA0: CTA1's V rows landed
+    uint64_t bar_v_full[kVStages];                 // CTA0: V rows of both CTAs landed (8 arrivals + 64 KB of TMA bytes)
     uint64_t bar_qk_done[kScStages];               // both: QK of tile g finished (ring by g % 4)
     uint64_t bar_pv_done[kScStages];               // both: PV of tile g finished
     uint64_t bar_pv_half[2];                       // both: first key half accumulated (64-key tiles)
@@ -243,6 +246,29 @@ template <bool DECODE> struct WorkIter {
     }
 };
 
+
+// Position in the sequence of 128-key tiles that a CTA pair walks: work item after work item.
+template <bool DECODE, int NT> struct TileCursor {
+    WorkIter<DECODE> it;
+    WorkItem w;
+    int t, ntiles;
+    bool live;
+    __device__ TileCursor(const AttnParams& params) : it(params), t(0), ntiles(0) { live = fetch(); }
+    __device__ bool fetch() {
+        while (it.template next<NT>(w)) {
+            ntiles = (w.blk_end - w.blk_begin + 1) / 2;
+            if (ntiles > 0) {   // empty items are never produced by the scheduler; skipping keeps the roles in step
+                t = 0;
+                return true;
+            }
+        }
+        return false;
+    }
+    __device__ void advance() {
+        if (++t >= ntiles) live = fetch();
+    }
+};
+
 // Key at position `j` (0..63) of 64-key block `blk` of a work item, in two steps so that callers can
 // keep the index load and the loads that depend on it in flight for different tiles.
 // Step 1: the raw index (-1 when the position does not exist).
@@ -251,6 +277,9 @@ __device__ __forceinline__ int key_index(const AttnParams& p, const WorkItem& w,
     if (blk >= w.blk_end) return -1;
     if constexpr (!DECODE) {
         const int pos = blk * 64 + j;
+#ifdef MXDSA_X_FAKEIDX
+        return pos < p.topk ? (int)(((unsigned)(pos + w.pair) * 40503u) & (unsigned)(p.s_kv - 1)) : -1;
+#endif
         return pos < p.topk ? __ldg(w.row + pos) : -1;
     } else {
         const bool extra = blk >= w.n_main_blocks;
@@ -275,7 +304,8 @@ __device__ __forceinline__ const uint8_t* key_resolve(const AttnParams& p, const
     } else {
         const bool extra = blk >= w.n_main_blocks;
         const int pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
-        valid = idx != -1 && pos < (extra ? w.elen : w.len);
+        // an index outside the pool (stale or corrupt) is treated like -1: not attended, nothing dereferenced
+        valid = idx >= 0 && idx < (extra ? p.extra_pool_rows : p.pool_rows) && pos < (extra ? w.elen : w.len);
         if (!valid) return nullptr;
         const unsigned psz = extra ? p.extra_page_size : p.page_size;
         const unsigned page = (unsigned)idx / psz, in_page = (unsigned)idx % psz;
@@ -288,6 +318,60 @@ template <bool DECODE>
 __device__ __forceinline__ const uint8_t* key_lookup(const AttnParams& p, const WorkItem& w, int blk, int j,
                                                      bool& valid, const uint8_t*& slot) {
     return key_resolve<DECODE>(p, w, blk, j, key_index<DECODE>(p, w, blk, j), valid, slot);
+}
+
+
+// Four consecutive positions j .. j+3 (j a multiple of 4) at once: one 16-byte load where the row allows it.
+template <bool DECODE>
+__device__ __forceinline__ int4 key_index4(const AttnParams& p, const WorkItem& w, int blk, int j) {
+    int4 r = make_int4(-1, -1, -1, -1);
+    if (blk >= w.blk_end) return r;
+    const int* row;
+    int pos, limit;
+    if constexpr (!DECODE) {
+        row = w.row;
+        pos = blk * 64 + j;
+        limit = p.topk;
+    } else {
+        const bool extra = blk >= w.n_main_blocks;
+        row = extra ? w.erow : w.row;
+        pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
+        limit = extra ? p.extra_topk : p.topk;
+    }
+    if (pos + 3 < limit && (reinterpret_cast<unsigned long long>(row + pos) & 15u) == 0) {
+        r = __ldg(reinterpret_cast<const int4*>(row + pos));
+    } else {
+        if (pos < limit) r.x = __ldg(row + pos);
+        if (pos + 1 < limit) r.y = __ldg(row + pos + 1);
+        if (pos + 2 < limit) r.z = __ldg(row + pos + 2);
+        if (pos + 3 < limit) r.w = __ldg(row + pos + 3);
+    }
+    return r;
+}
+// Row coordinates of those four keys in the 2-D view {512 B, rows} of their KV store (-1 = no row), and the
+// tensor map of that store.
+template <bool DECODE>
+__device__ __forceinline__ const void* key_rows4(const AttnParams& p, const TensorMaps& maps, const WorkItem& w, int blk,
+                                                 int j, int4 ix, int (&r)[4]) {
+    const int id[4] = {ix.x, ix.y, ix.z, ix.w};
+    if constexpr (!DECODE) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r[i] = (blk < w.blk_end && id[i] >= 0 && id[i] < p.s_kv) ? id[i] : -1;
+        return &maps.kv;
+    } else {
+        const bool extra = blk >= w.n_main_blocks;
+        const int pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
+        const int len = extra ? w.elen : w.len;
+        const unsigned psz = extra ? p.extra_page_size : p.page_size;
+        const unsigned rpb = extra ? p.extra_rows_per_block : p.rows_per_block;
+        const long long pool = extra ? p.extra_pool_rows : p.pool_rows;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const bool ok = blk < w.blk_end && id[i] >= 0 && id[i] < pool && pos + i < len;
+            r[i] = ok ? (int)(((unsigned)id[i] / psz) * rpb + (unsigned)id[i] % psz) : -1;
+        }
+        return extra ? &maps.ekv : &maps.kv;
+    }
 }
 
 // packed fp32 pairs (one instruction for two lanes of data)
@@ -317,6 +401,10 @@ __device__ __forceinline__ float2 f2_add(float2 a, float2 b) {
 // 16-byte asynchronous copy global -> shared; `bytes` = 16 copies, 0 writes zeros.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// 8-byte flavour (through L1; the 16-byte one is the only size that may bypass it)
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 // one arrival on `bar` once all cp.async issued so far by this thread have landed
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
@@ -366,9 +454,17 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 #define MXDSA_EV_MASK 0xffffffu
 #endif
 // event trace: cycle stamps of tiles 16..31 of this CTA (profiling builds only)
+#ifdef MXDSA_X_WARPEV
+#define MXDSA_EV(gtile, id)
+#define MXDSA_EVW(gtile, id) \
+    if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
+#else
+#define MXDSA_EVW(gtile, id)
 #define MXDSA_EV(gtile, id) \
     if ((((MXDSA_EV_MASK) >> (id)) & 1u) && (gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
+#endif
 #else
+#define MXDSA_EVW(gtile, id)
 #define MXDSA_PROF_BEGIN
 #define MXDSA_PROF_END(code)
 #define MXDSA_EV(gtile, id)
@@ -448,12 +544,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         mbar_init(smem_u32(&sm.bar_q_full), 2);
         mbar_init(smem_u32(&sm.bar_q_empty), 2);
         for (int i = 0; i < kKStages; ++i) {
-            mbar_init(smem_u32(&sm.bar_k_landed[i]), 128);
+            mbar_init(smem_u32(&sm.bar_k_landed[i]), 128 + 4);   // 128 copy completions + one plain arrival per producer warp
             mbar_init(smem_u32(&sm.bar_k_full[i]), 1);
         }
         for (int i = 0; i < kVStages; ++i) {
-            mbar_init(smem_u32(&sm.bar_v_landed[i]), 128);
-            mbar_init(smem_u32(&sm.bar_v_full[i]), 1);
+            mbar_init(smem_u32(&sm.bar_v_full[i]), 8);
         }
         for (int i = 0; i < kScStages; ++i) {
             mbar_init(smem_u32(&sm.bar_qk_done[i]), 1);
@@ -481,19 +576,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #ifdef MXDSA_PROFILE
     const long long prof_kernel_t0 = clock64();
 #endif
-    if (warp == 11) {
-        // V dimension scales: rows 0-31 feed lane quadrants 0,1 (dims of CTA 0 = w1), rows 32-63
-        // quadrants 2,3 (dims of CTA 1 = w2); every row of a group is the same four words.
-        for (int i = lane; i < 64; i += 32) {
-            const uint32_t* w = i < 32 ? p.w1 : p.w2;
-            for (int c = 0; c < 4; ++c) {
-                sm.v_sf[0][i * 4 + c] = w[c];
-                sm.v_sf[1][i * 4 + c] = w[4 + c];
-            }
-        }
-        fence_proxy_async_smem();
-        if (lane == 0) prefetch_tensormap(&maps.q);
-    }
+    if (warp == 11 && lane == 0) prefetch_tensormap(&maps.q);
     __syncthreads();
     cluster_sync();
     if (warp == 10) {
@@ -505,6 +588,21 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     cluster_sync();
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
+    if (warp >= 12 && warp < 16) {
+        // V dimension scales (B-operand scale columns of every PV): lanes 0-63 hold the dims of CTA 0's half
+        // (w1), lanes 64-127 those of CTA 1's half (w2); column c = word c.  Written once, straight from
+        // registers; the barriers below order it before the first MMA of either CTA.
+        const uint32_t* wv = (warp & 3) < 2 ? p.w1 : p.w2;
+        uint32_t v[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v[c] = wv[c];
+        tmem_st8(tmem + (uint32_t((warp & 3) * 32) << 16) + kColVs, v);
+        tmem_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    tc_fence_after();
 
     const uint64_t desc_k128 = smem_desc_base(16, 1024, 2);   // K-major, 128-byte swizzle
     const uint64_t desc_v = smem_desc_base(16384, 1024, 2);   // MN-major, 128-byte swizzle
@@ -525,60 +623,96 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                   "register budget must add up to the launch allocation exactly");
     if (warp < 8) {
         if constexpr (kRebalanceRegs) setmaxnreg_dec<kRegsCopy>();
-        // ===================== K producers (warps 0-3) and V producers (warps 4-7) =====================
-        // One instruction stream for both (the instruction cache is the scarce resource here); what
-        // differs is data.  K producer pw: keys 64*cta + 16*pw + i (i < 16) of the tile, whole 512-byte
-        // rows, one row per instruction; lane L writes byte chunk L of the row -> chunk tile L/8,
-        // 16-byte column (L%8) ^ (row%8).  V producer pw: keys 32*pw + 2i, 2i+1, bytes 256*cta..+255,
-        // two rows per instruction; lane L writes chunk tile (L%16)/8 of key 2i + L/16.
-        const bool isv = warp >= 4;
-        const int pw = warp & 3;
-        const int key = isv ? 32 * pw + lane : 64 * (int)cta + 16 * pw + (lane & 15);   // address this lane looks up
-        const int sel_mul = isv ? 2 : 1, sel_add = isv ? lane / 16 : 0;                 // source lane of iteration i
-        const int row0 = isv ? 32 * pw + lane / 16 : 16 * pw;                           // tile row of iteration 0
-        const uint32_t src_off = isv ? 256u * cta + (lane & 15) * 16 : lane * 16;
-        const uint32_t stage0 = isv ? smem_u32(sm.v[0]) + ((lane & 15) / 8) * 16384 : smem_u32(sm.k[0]) + (lane / 8) * 8192;
-        const uint32_t landed0 = isv ? smem_u32(&sm.bar_v_landed[0]) : smem_u32(&sm.bar_k_landed[0]);
-        const uint32_t done0 = isv ? smem_u32(&sm.bar_pv_done[0]) : smem_u32(&sm.bar_qk_done[0]);
-        const uint32_t nstages = isv ? kVStages : kKStages;
-        WorkIter<DECODE> it(p);
-        WorkItem w;
-        uint32_t gt = 0;  // tiles issued so far
-        uint32_t s = 0;   // gt % nstages
+        if (warp < 4) {
+            // ===================== K producers (warps 0-3): 16-byte cp.async =====================
+            // Warp pw copies rows 64*cta + 16*pw + i (i < 16) of every tile, whole 512-byte rows, one row per
+            // instruction: lane L writes byte chunk L of the row -> chunk tile L/8, 16-byte column (L%8) ^ (row%8).
+            // It also gathers the 8 scale bytes of 32 keys of the tile (its own 16 and the matching 16 of the
+            // peer CTA's half) into sm.kslot: every CTA needs the scales of all 128 keys.
+            // Raw indices are loaded one tile ahead and turned into addresses only when the tile is copied: a warp
+            // issues in order, so an address computed at load time would hold the warp until the load is back.
+            const int pw = warp;
+            const int key = lane < 16 ? 64 * (int)cta + 16 * pw + lane : 64 * (1 - (int)cta) + 16 * pw + (lane - 16);
+            TileCursor<DECODE, NT> ck(p);
+            uint32_t kt = 0;
+            int idx = ck.live ? key_index<DECODE>(p, ck.w, ck.w.blk_begin + 2 * ck.t + key / 64, key % 64) : -1;
+            const uint32_t k_stage0 = smem_u32(sm.k[0]) + (lane / 8) * 8192;
 #pragma unroll 1
-        while (it.template next<NT>(w)) {
-            const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
-            if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-            // iteration t looks up the row addresses of tile t+1 (one look-up site) and copies tile t
-            const uint8_t* ptr = nullptr;
-#pragma unroll 1
-            for (int t = -1; t < ntiles; ++t) {
-                const uint8_t* ptr_next = nullptr;
-                if (t + 1 < ntiles) {
+            while (ck.live) {
+                const uint32_t s = kt % kKStages;
+                if (kt >= (uint32_t)kKStages) {   // stage s was last used by tile kt-2: its QK must be done
+                    const uint32_t g = kt - kKStages;
+                    MXDSA_WAIT(sm.bar_qk_done[g % kScStages], (g / kScStages) & 1, 10);
+                }
+                if (pw == 0 && lane == 0) { MXDSA_EV(kt, 0) }
+                const uint8_t* cur;
+                const uint8_t* slot;
+                uint32_t vbits;
+                {
                     bool valid;
-                    const uint8_t* slot;
-                    ptr_next = key_lookup<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + key / 64, key % 64, valid, slot);
+                    cur = key_resolve<DECODE>(p, ck.w, ck.w.blk_begin + 2 * ck.t + key / 64, key % 64, idx, valid, slot);
+                    vbits = __ballot_sync(0xffffffffu, valid);
                 }
-                if (t >= 0) {
-                    if (gt >= nstages) {   // stage s was last used by tile gt - nstages: its MMAs must be done
-                        const uint32_t g = gt - nstages;
-                        MXDSA_WAIT_ADDR_(-1, done0 + (g % kScStages) * 8, (g / kScStages) & 1, 10);
-                    }
-                    if ((warp & 3) == 0 && lane == 0) { MXDSA_EV(gt, isv ? 2 : 0) }
-                    const uint32_t base = stage0 + s * 32768;
-#pragma unroll 2
-                    for (int i = 0; i < 16; ++i) {
-                        const uint8_t* src = reinterpret_cast<const uint8_t*>(
-                            __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr), sel_mul * i + sel_add));
-                        const int r = row0 + sel_mul * i;
-                        cp_async16(base + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + src_off : p.kv, src ? 16u : 0u);
-                    }
-                    cp_async_arrive(landed0 + s * 8);
-                    if ((warp & 3) == 0 && lane == 0) { MXDSA_EV(gt, isv ? 3 : 1) }
-                    s = s + 1 == nstages ? 0 : s + 1;
-                    ++gt;
+                // the next tile's indices: the loads run while this tile's rows are issued
+                ck.advance();
+                idx = ck.live ? key_index<DECODE>(p, ck.w, ck.w.blk_begin + 2 * ck.t + key / 64, key % 64) : -1;
+                const uint32_t base = k_stage0 + s * 32768;
+#pragma unroll 4
+                for (int i = 0; i < 16; ++i) {
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(cur), i));
+                    const int r = 16 * pw + i;
+                    cp_async16(base + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + lane * 16 : p.kv, src ? 16u : 0u);
                 }
-                ptr = ptr_next;
+                cp_async8(smem_u32(&sm.kslot[s][key]), slot ? slot : p.kv, slot ? 8u : 0u);
+                cp_async_arrive(smem_u32(&sm.bar_k_landed[s]));
+                if (lane == 0) {   // validity of the warp's 32 keys: a plain store, released by a plain arrival
+                    sm.kvalid[s][4 * cta + pw] = (uint16_t)vbits;
+                    sm.kvalid[s][4 * (1 - cta) + pw] = (uint16_t)(vbits >> 16);
+                    mbar_arrive(smem_u32(&sm.bar_k_landed[s]));
+                }
+                if (pw == 0 && lane == 0) { MXDSA_EV(kt, 1) }
+                ++kt;
+            }
+        } else {
+            // ===================== V producers (warps 4-7): TMA gather4 =====================
+            // CTA c stages bytes 256c .. 256c+255 of all 128 keys of a tile as [chunk of 128 B][key][128 B].
+            // Warp pw takes keys 32*pw .. 32*pw+31; its lanes 0-7 own four keys each and issue two gather4
+            // copies (one per chunk) of four rows (measured: the copy engine takes requests fastest from a few
+            // lanes of several warps -- 4 warps x 8 lanes reach 21 B/clk, one warp of 32 lanes 8 B/clk).  Rows
+            // that do not exist (index -1, position beyond the list, row outside the store) get a coordinate
+            // outside the tensor map, which the copy engine fills with zeros.  The bytes of both CTAs complete
+            // on ONE barrier of CTA 0, where the PV issuer waits; nothing else needs to know that V has landed.
+            const int pw = warp - 4;
+            const int j0 = 32 * pw + 4 * (lane & 7);     // first of this lane's four keys in the tile
+            TileCursor<DECODE, NT> cv(p);
+            uint32_t vt = 0;
+            int4 ix = make_int4(-1, -1, -1, -1);
+            if (cv.live) ix = key_index4<DECODE>(p, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64);
+            const uint32_t v_full0 = map_to_cta(smem_u32(&sm.bar_v_full[0]), 0);
+            const uint32_t v_dst0 = smem_u32(sm.v[0]) + j0 * 128;
+#pragma unroll 1
+            while (cv.live) {
+                const uint32_t s = vt % kVStages;
+                if (vt >= (uint32_t)kVStages) {   // stage s was last used by tile vt-3: its PV must be done
+                    const uint32_t g = vt - kVStages;
+                    MXDSA_WAIT(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 11);
+                }
+                if (pw == 0 && lane == 0) { MXDSA_EV(vt, 2) }
+                int r[4];
+                const void* map = key_rows4<DECODE>(p, maps, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64, ix, r);
+                cv.advance();
+                if (cv.live) ix = key_index4<DECODE>(p, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64);
+                if (lane == 0) mbar_expect_tx_cluster(v_full0 + s * 8, 2 * 32 * 128);
+                __syncwarp();
+                if (lane < 8) {
+                    const uint32_t dst = v_dst0 + s * 32768;
+                    tma_gather4_pair(dst, map, 256 * (int)cta, r[0], r[1], r[2], r[3], v_full0 + s * 8, kEvictLast);
+                    tma_gather4_pair(dst + 16384, map, 256 * (int)cta + 128, r[0], r[1], r[2], r[3], v_full0 + s * 8, kEvictLast);
+                }
+                __syncwarp();
+                if (pw == 0 && lane == 0) { MXDSA_EV(vt, 3) }
+                ++vt;
             }
         }
     } else if (warp < 12) {
@@ -624,7 +758,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     if (elect_one()) {
                         if (!mine)   // first own tile of this pair: the pair's Q scale rows
                             tmem_cp_sf_pair(sfa0, smem_desc(desc_sf, smem_u32(sm.q_sf)));
-                        tmem_cp_sf_pair(sfb0, smem_desc(desc_sf, smem_u32(sm.k_sf[sc])));
+                        tmem_cp_sf_pair(sfb0, smem_desc(desc_sf, smem_u32(sm.k_sf[s])));
                         const uint64_t b_base = smem_desc(desc_k128, smem_u32(sm.k[s]));
 #pragma unroll
                         for (int kk = 0; kk < 16; ++kk) {
@@ -668,7 +802,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #pragma unroll 1
                 for (int t = 0; t < ntiles; ++t, ++gt) {
                     const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
-                    MXDSA_WAIT_THREAD(sm.bar_k_landed[s], ph, 12);
+                    MXDSA_WAIT_TIGHT(sm.bar_k_landed[s], ph, 12);
                     fence_proxy_async_smem();
                     mbar_arrive_cluster(k_full0 + s * 8);
                 }
@@ -682,11 +816,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             uint32_t gt = 0, gw = 0;
             const uint32_t pv_half_peer = map_to_cta(smem_u32(&sm.bar_pv_half[0]), 1);
             const uint32_t pv_done_peer = map_to_cta(smem_u32(&sm.bar_pv_done[0]), 1);
-            if (elect_one()) {
-                tmem_cp_sf_pair(tmem + kColVs, smem_desc(desc_sf, smem_u32(sm.v_sf[0])));
-                tmem_cp_sf_pair(tmem + kColVs + 4, smem_desc(desc_sf, smem_u32(sm.v_sf[1])));
-            }
-            __syncwarp();
 #pragma unroll 1
             while (it.template next<NT>(w)) {
                 const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
@@ -698,9 +827,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
                     const uint32_t b = gt & 1, bph = (gt >> 1) & 1;
                     const uint32_t sc = gt % kScStages;
-                    MXDSA_WAIT_TIGHT(sm.bar_v_landed[s], ph, 31);
                     MXDSA_WAIT_TIGHT(sm.bar_v_full[s], ph, 34);
-                    fence_proxy_async_smem();
                     const uint64_t a_base = smem_desc(desc_k128, smem_u32(sm.s[b]));
                     const uint64_t b_base = smem_desc(desc_v, smem_u32(sm.v[s]));
                     const uint32_t sfa = tmem + kColSs + 4 * b;
@@ -710,6 +837,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                         if (NT == 128 && h == 0) continue;   // 128-key tiles: one wait, after both halves are in
                         MXDSA_WAIT_TIGHT(sm.bar_s_full[b][h], bph, 32 + h);
                         MXDSA_EV(gt, 13 + h)
+                        MXDSA_EVW(gt, 16)
                         tc_fence_after();
                         __syncwarp();
                         if (elect_one()) {
@@ -735,24 +863,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     MXDSA_EV(gt, 15)
                 }
                 ++gw;
-            }
-        } else if (cta == 1 && lane == 0) {
-            // ===================== V relay (CTA 1) =====================
-            WorkIter<DECODE> it(p);
-            WorkItem w;
-            uint32_t gt = 0;
-            const uint32_t v_full0 = map_to_cta(smem_u32(&sm.bar_v_full[0]), 0);
-#pragma unroll 1
-            while (it.template next<NT>(w)) {
-                const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
-                if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-#pragma unroll 1
-                for (int t = 0; t < ntiles; ++t, ++gt) {
-                    const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
-                    MXDSA_WAIT_THREAD(sm.bar_v_landed[s], ph, 13);
-                    fence_proxy_async_smem();
-                    mbar_arrive_cluster(v_full0 + s * 8);
-                }
             }
         }
     } else if (warp == 11) {
@@ -790,57 +900,37 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 fence_proxy_async_smem();
                 __syncwarp();
             }
-            // ---- per tile: K scale rows, key token scales, validity.  Two loads deep: while tile t is
-            // published, the scale slots of tile t+1 and the indices of tile t+2 are in flight.
-            // lane L looks after keys L, L+32 (block 0) and L+64, L+96 (block 1) of a tile.
-            int ix[4] = {-1, -1, -1, -1};
-            uint2 sv_next[4] = {};
-            uint32_t vb_next[4] = {};
+            // ---- per tile: K scale rows, key token scales, validity.  Everything arrives in shared memory with the
+            // K rows (the producers gather the scale slots and vote the validity bits), so no global load sits
+            // between "K landed" and "QK may start".  lane L looks after keys L, L+32 (block 0) and L+64, L+96.
 #pragma unroll 1
-            for (int t = -2; t < ntiles; ++t) {
-                uint2 sv[4];
-                uint32_t vbits[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    sv[j] = sv_next[j];
-                    vbits[j] = vb_next[j];
-                }
-                if (t + 1 >= 0 && t + 1 < ntiles) {   // scale slots of tile t+1 (its indices arrived during the last iteration)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        bool valid;
-                        const uint8_t* slot;
-                        key_resolve<DECODE>(p, w, w.blk_begin + 2 * (t + 1) + j / 2, (j % 2) * 32 + lane, ix[j], valid, slot);
-                        sv_next[j] = slot != nullptr ? __ldg(reinterpret_cast<const uint2*>(slot)) : make_uint2(0u, 0u);
-                        vb_next[j] = __ballot_sync(0xffffffffu, valid);
-                    }
-                }
-                if (t + 2 < ntiles) {   // indices of tile t+2
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        ix[j] = key_index<DECODE>(p, w, w.blk_begin + 2 * (t + 2) + j / 2, (j % 2) * 32 + lane);
-                }
-                if (t < 0) continue;
+            for (int t = 0; t < ntiles; ++t) {
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
-                if (gt >= kScStages) {   // the stage was last used by tile gt-4: its cp and its readers are done
-                    MXDSA_WAIT(sm.bar_qk_done[sc], sph ^ 1, 42);
-                    MXDSA_WAIT(sm.bar_tok_empty[sc], sph ^ 1, 43);
-                }
+                const uint32_t ks = gt % kKStages;
+                MXDSA_EV(gt, 13)
+                MXDSA_WAIT_TIGHT(sm.bar_k_landed[ks], (gt / kKStages) & 1, 44);
+                MXDSA_EV(gt, 5)
+                uint2 sv[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sv[j] = sm.kslot[ks][j * 32 + lane];
+                const uint32_t vword = reinterpret_cast<const uint32_t*>(sm.kvalid[ks])[lane & 3];
                 // rows for tcgen05.cp: row r = (half of the tile)*32 + L holds keys (half*64 + L) and (+32):
-                // {bytes0-3[k0], bytes0-3[k1], bytes4-7[k0], bytes4-7[k1]}
-                *reinterpret_cast<uint4*>(&sm.k_sf[sc][lane * 4]) = make_uint4(sv[0].x, sv[1].x, sv[0].y, sv[1].y);
-                *reinterpret_cast<uint4*>(&sm.k_sf[sc][(32 + lane) * 4]) = make_uint4(sv[2].x, sv[3].x, sv[2].y, sv[3].y);
+                // {bytes0-3[k0], bytes0-3[k1], bytes4-7[k0], bytes4-7[k1]}.  The rows of K stage ks were last read
+                // by the QK of tile gt-2, which finished before the stage was refilled.
+                *reinterpret_cast<uint4*>(&sm.k_sf[ks][lane * 4]) = make_uint4(sv[0].x, sv[1].x, sv[0].y, sv[1].y);
+                *reinterpret_cast<uint4*>(&sm.k_sf[ks][(32 + lane) * 4]) = make_uint4(sv[2].x, sv[3].x, sv[2].y, sv[3].y);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(sc_full0 + sc * 8);
+                MXDSA_EV(gt, 4)
+                // what the softmax warps read: ring of 4, a stage is free once the softmax of tile gt-4 is through
+                if (gt >= kScStages) MXDSA_WAIT(sm.bar_tok_empty[sc], sph ^ 1, 43);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                     sm.tok_scale[sc][j * 32 + lane] = __uint_as_float((sv[j].x & 0xffu) << 23);
-                if (lane < 4) sm.valid[sc][lane] = lane == 0 ? vbits[0] : lane == 1 ? vbits[1] : lane == 2 ? vbits[2] : vbits[3];
-                fence_proxy_async_smem();
+                if (lane < 4) sm.valid[sc][lane] = vword;
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(smem_u32(&sm.bar_tok_full[sc]));
-                    mbar_arrive_cluster(sc_full0 + sc * 8);
-                }
-                MXDSA_EV(gt, 4)
+                if (lane == 0) mbar_arrive(smem_u32(&sm.bar_tok_full[sc]));
                 if (t == 0) {   // the pair's Q tile: its latency hides behind the first tile's staging
                     MXDSA_WAIT(sm.bar_q_landed, gw & 1, 41);
                     if (lane == 0) mbar_arrive_cluster(q_full0);
@@ -971,11 +1061,17 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                         float am = 0.f;
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
+#ifdef MXDSA_X_NOTOK
+                            const float4 tk = make_float4(1.f, 1.f, 1.f, 1.f);
+#else
                             const float4 tk = tok4[g * 8 + i / 4];
+#endif
                             float2 a = f2_fma(make_float2(x[i], x[i + 1]), scale2, negm2);
                             float2 c = f2_fma(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
+#ifndef MXDSA_X_NOEX2
                             a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
                             c = make_float2(ex2_approx(c.x), ex2_approx(c.y));
+#endif
                             sum2[0] = f2_add(sum2[0], a);
                             sum2[1] = f2_add(sum2[1], c);
                             a = f2_mul(a, make_float2(tk.x, tk.y));
@@ -993,7 +1089,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                         for (int i = 0; i < 32; i += 4) {
                             const float2 a = f2_mul(make_float2(x[i], x[i + 1]), mul2);
                             const float2 c = f2_mul(make_float2(x[i + 2], x[i + 3]), mul2);
+#ifdef MXDSA_X_NOCVT
+                            s8[i / 4] = __float_as_uint(a.x) ^ __float_as_uint(a.y) ^ __float_as_uint(c.x) ^ __float_as_uint(c.y);
+#else
                             s8[i / 4] = (uint32_t)cvt_e4m3x2(a.x, a.y) | ((uint32_t)cvt_e4m3x2(c.x, c.y) << 16);
+#endif
                         }
                     }
                     e_bytes |= e << (8 * g);
@@ -1018,7 +1118,12 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 }
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 11) }
                 // O rescale before the first key half is accumulated (this thread: its whole lane)
-                if (grow0 && t > 0) {
+#ifndef MXDSA_X_NORESCALE
+                if (grow0 && t > 0)
+#else
+                if (false)
+#endif
+                {
                     MXDSA_WAIT_POLL(sm.bar_pv_done[(gt - 1) % kScStages], ((gt - 1) / kScStages) & 1, 53);
                     tc_fence_after();
                     rescale_o(lane_addr, scale0);
@@ -1152,7 +1257,10 @@ done:
     if (p.prof != nullptr && blockIdx.x < 2 && blockIdx.y == 0 && threadIdx.x < 64) {
         if (threadIdx.x == 0) sm.prof[0] = (unsigned long long)(clock64() - prof_kernel_t0);
         p.prof[blockIdx.x * 64 + threadIdx.x] = sm.prof[threadIdx.x];
-        if (blockIdx.x == 0)
+#ifndef MXDSA_EV_CTA
+#define MXDSA_EV_CTA 0
+#endif
+        if (blockIdx.x == MXDSA_EV_CTA)
             for (int i = threadIdx.x; i < 384; i += 64) p.prof[128 + i] = (unsigned long long)(unsigned)(&sm.ev[0][0])[i];
     }
 #endif

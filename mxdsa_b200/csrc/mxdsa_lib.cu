@@ -91,6 +91,24 @@ int make_q_map(CUtensorMap* map, const void* base, uint64_t tokens, uint64_t req
     return MXDSA_OK;
 }
 
+// 2-D map over the data rows of a KV store viewed as rows of 512 bytes (prefill: the token rows; decode:
+// the whole pool, whose pages start on multiples of 512 bytes, so that row = page * (stride / 512) + slot).
+// One gather4 box = 4 rows x 128 bytes, landing as four 128-byte-swizzled rows.
+int make_kv_map(CUtensorMap* map, const void* base, uint64_t rows) {
+    cuuint64_t dims[2] = {512, rows};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, 1};
+    cuuint32_t es[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, es,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tl_last_cuda_error = (int)r;
+        return MXDSA_ERR_CUDA;
+    }
+    return MXDSA_OK;
+}
+
 constexpr size_t kSmemBytes = sizeof(mxdsa::SmemPlan) + 1024;
 
 template <typename K>
@@ -341,6 +359,8 @@ int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     memset(&maps, 0, sizeof(maps));
     st = make_q_map(&maps.q, p->q, (uint64_t)p->s_q, 1, (uint64_t)p->stride_q_token, (uint64_t)ap.stride_q_b);
     if (st != MXDSA_OK) return st;
+    st = make_kv_map(&maps.kv, p->kv, (uint64_t)p->s_kv);
+    if (st != MXDSA_OK) return st;
 
     const int clusters = ap.num_pairs < d->sm_count / 2 ? ap.num_pairs : d->sm_count / 2;
     const dim3 grid(2 * clusters, 1, 1);
@@ -439,6 +459,8 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
         ap.eidx_stride_b = p->stride_extra_indices_b;
         ap.extra_topk_length = p->extra_topk_length;
     }
+    ap.pool_rows = (long long)p->num_blocks * p->page_block_size;
+    ap.extra_pool_rows = has_extra ? (long long)p->extra_num_blocks * p->extra_page_block_size : 0;
     ap.sched_meta = p->sched_meta;
     ap.num_splits = p->num_splits;
     ap.o_accum = o_accum;
@@ -449,6 +471,15 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
     st = make_q_map(&maps.q, p->q, (uint64_t)p->s_q, (uint64_t)p->b, (uint64_t)p->stride_q_s,
                     p->b > 1 ? (uint64_t)p->stride_q_b : (uint64_t)p->stride_q_s * p->s_q);
     if (st != MXDSA_OK) return st;
+    // the last page of a pool may be shorter than the page stride: only its data rows are in the view
+    st = make_kv_map(&maps.kv, p->kv,
+                     (uint64_t)(p->num_blocks - 1) * (uint64_t)ap.rows_per_block + (uint64_t)p->page_block_size);
+    if (st != MXDSA_OK) return st;
+    if (has_extra) {
+        st = make_kv_map(&maps.ekv, p->extra_kv, (uint64_t)(p->extra_num_blocks - 1) * (uint64_t)ap.extra_rows_per_block +
+                                                     (uint64_t)p->extra_page_block_size);
+        if (st != MXDSA_OK) return st;
+    }
 
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
     const dim3 grid(2 * ((p->s_q + 1) / 2), p->num_sm_parts, 1);
