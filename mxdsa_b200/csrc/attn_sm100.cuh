@@ -419,6 +419,20 @@ template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
 
 // multiply the 256 O columns of this thread's tensor-memory lane by f (out of line: one copy)
 __device__ __noinline__ void rescale_o(uint32_t lane_addr, float f) {
+#ifdef MXDSA_RESCALE_WIDE
+    // 64 columns per round: half as many exposed load latencies
+#pragma unroll 1
+    for (int c = 0; c < 256; c += 64) {
+        uint32_t v[64];
+        tmem_ld32(lane_addr + kColO + c, v);
+        tmem_ld32(lane_addr + kColO + c + 32, v + 32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 64; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+        tmem_st32(lane_addr + kColO + c, v);
+        tmem_st32(lane_addr + kColO + c + 32, v + 32);
+    }
+#else
 #pragma unroll 1
     for (int c = 0; c < 256; c += 32) {
         uint32_t v[32];
@@ -428,6 +442,7 @@ __device__ __noinline__ void rescale_o(uint32_t lane_addr, float f) {
         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
         tmem_st32(lane_addr + kColO + c, v);
     }
+#endif
     tmem_wait_st();
 }
 // one 32-byte store (a whole sector); the address must be 32-byte aligned
@@ -456,15 +471,22 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 // event trace: cycle stamps of tiles 16..31 of this CTA (profiling builds only)
 #ifdef MXDSA_X_WARPEV
 #define MXDSA_EV(gtile, id)
+#define MXDSA_EVW2(gtile, id)
 #define MXDSA_EVW(gtile, id) \
     if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
 #else
 #define MXDSA_EVW(gtile, id)
+#ifdef MXDSA_X_QKEV
+#define MXDSA_EVW2(gtile, id) if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
+#else
+#define MXDSA_EVW2(gtile, id)
+#endif
 #define MXDSA_EV(gtile, id) \
     if ((((MXDSA_EV_MASK) >> (id)) & 1u) && (gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
 #endif
 #else
 #define MXDSA_EVW(gtile, id)
+#define MXDSA_EVW2(gtile, id)
 #define MXDSA_PROF_BEGIN
 #define MXDSA_PROF_END(code)
 #define MXDSA_EV(gtile, id)
@@ -616,7 +638,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     // Each setmaxnreg is executed by the four warps of one aligned warp group with the same value.
     // Measured: prefill gains 8%, decode (short work items, heavier address arithmetic in the copy
     // warps) loses 15%, so only prefill rebalances.
+#ifdef MXDSA_X_REBAL_ALL
+    constexpr bool kRebalanceRegs = true;
+#else
     constexpr bool kRebalanceRegs = !DECODE;
+#endif
     constexpr int kRegsCopy = MXDSA_REGS_COPY, kRegsCtl = MXDSA_REGS_CTL;
     constexpr int kRegsSoftmax = (kThreads * 96 - 8 * 32 * kRegsCopy - 4 * 32 * kRegsCtl) / (8 * 32);
     static_assert(kRegsSoftmax % 8 == 0 && 8 * 32 * kRegsCopy + 4 * 32 * kRegsCtl + 8 * 32 * kRegsSoftmax == kThreads * 96,
@@ -748,8 +774,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                     const uint32_t bph = (gt >> 1) & 1;
                     MXDSA_WAIT_TIGHT(sm.bar_sc_full[sc], sph, 21);
+                    MXDSA_EVW2(gt, 16)
                     MXDSA_WAIT_TIGHT(sm.bar_p_empty[e], bph ^ 1, 22);
+                    MXDSA_EVW2(gt, 17)
                     MXDSA_WAIT_TIGHT(sm.bar_k_landed[s], ph, 23);
+                    MXDSA_EVW2(gt, 18)
                     MXDSA_WAIT_TIGHT(sm.bar_k_full[s], ph, 24);
                     fence_proxy_async_smem();   // rows written by cp.async are read by the tensor core
                     MXDSA_EV(gt, 6)
@@ -1053,6 +1082,45 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 uint8_t* srow = sm.s[b];
                 float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
                 uint32_t e_bytes = 0;
+#ifdef MXDSA_EXP_UNROLLED
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t s8[8];
+                    uint32_t e;
+                    float am0 = 0.f, am1 = 0.f;
+                    float* xg = x + 32 * g;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 tk = tok4[g * 8 + i / 4];
+                        float2 a = f2_fma(make_float2(xg[i], xg[i + 1]), scale2, negm2);
+                        float2 c = f2_fma(make_float2(xg[i + 2], xg[i + 3]), scale2, negm2);
+                        a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
+                        c = make_float2(ex2_approx(c.x), ex2_approx(c.y));
+                        sum2[0] = f2_add(sum2[0], a);
+                        sum2[1] = f2_add(sum2[1], c);
+                        a = f2_mul(a, make_float2(tk.x, tk.y));
+                        c = f2_mul(c, make_float2(tk.z, tk.w));
+                        am0 = fmax3(am0, a.x, a.y);
+                        am1 = fmax3(am1, c.x, c.y);
+                        xg[i] = a.x; xg[i + 1] = a.y; xg[i + 2] = c.x; xg[i + 3] = c.y;
+                    }
+                    const float am = fmaxf(am0, am1);
+                    e = cvt_ue8m0_roundup(am > 0.f ? __fdividef(am, 448.0f) : 1.0f);
+                    e = max(e, 61u);
+                    const float mulf = __uint_as_float((254u - e) << 23);
+                    const float2 mul2 = make_float2(mulf, mulf);
+                    if (g == 0 && warp == 12 && lane == 0) { MXDSA_EV(gt, 18) }
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float2 a = f2_mul(make_float2(xg[i], xg[i + 1]), mul2);
+                        const float2 c = f2_mul(make_float2(xg[i + 2], xg[i + 3]), mul2);
+                        s8[i / 4] = (uint32_t)cvt_e4m3x2(a.x, a.y) | ((uint32_t)cvt_e4m3x2(c.x, c.y) << 16);
+                    }
+                    e_bytes |= e << (8 * g);
+                    *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + g * 32)) = make_uint4(s8[0], s8[1], s8[2], s8[3]);
+                    *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + g * 32 + 16)) = make_uint4(s8[4], s8[5], s8[6], s8[7]);
+                }
+#else
 #pragma unroll 1
                 for (int g = 0; g < 2; ++g) {
                     uint32_t s8[8];
@@ -1104,6 +1172,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                         for (int i = 0; i < 32; ++i) x[i] = x[32 + i];
                     }
                 }
+#endif
                 // scale rows: row (row%32) and its copy at +32; word row/32; bytes 2*half, 2*half+1
                 reinterpret_cast<uint16_t*>(&sm.s_sf[b][(row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
                 reinterpret_cast<uint16_t*>(&sm.s_sf[b][(32 + row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
