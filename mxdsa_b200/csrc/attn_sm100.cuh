@@ -53,11 +53,13 @@
 
 #include "sm100_ptx.cuh"
 
-#ifndef MXDSA_REGS_COPY
-#define MXDSA_REGS_COPY 64
+
+#ifndef MXDSA_V_HINT
+#define MXDSA_V_HINT kEvictLast
 #endif
-#ifndef MXDSA_REGS_CTL
-#define MXDSA_REGS_CTL 64
+#ifndef MXDSA_K_STAGES
+#define MXDSA_K_STAGES 3
+#define MXDSA_V_STAGES 2
 #endif
 
 namespace mxdsa {
@@ -68,11 +70,14 @@ static constexpr int kHeads = 64;
 static constexpr int kDim = 512;
 static constexpr int kRowBytes = 528;
 static constexpr int kTileKeys = 128;    // keys per tensor-core tile
-static constexpr int kKStages = 2;       // K ring depth (32 KB per stage and CTA); freed as soon as QK is done
-static constexpr int kVStages = 3;       // V ring depth (32 KB per stage and CTA); held until PV is done
+static constexpr int kKStages = MXDSA_K_STAGES;       // K ring depth (32 KB per stage and CTA); freed as soon as QK is done
+static constexpr int kVStages = MXDSA_V_STAGES;       // V ring depth (32 KB per stage and CTA); held until PV is done
 static constexpr int kScStages = 4;      // scale/validity ring depth; also the depth of the
                                          // per-tile "QK done" / "PV done" barrier rings
-static constexpr int kThreads = 640;
+// registers per thread that a launch of 384 + 128 G threads gets (65536 / threads, rounded down to a multiple of 8)
+__host__ __device__ constexpr int launch_regs(int g) { return g == 2 ? 96 : 80; }
+static constexpr int kBaseThreads = 384;   // warps 0-11: K producers, V producers, control; then G x 4 softmax warps
+static constexpr int kMaxGroups = 3;     // softmax groups of four warps (template parameter G = 2 or 3); tile g is handled by group g % G
 
 // tensor-memory columns
 static constexpr uint32_t kColO = 0;      // 256 columns
@@ -123,6 +128,7 @@ struct AttnParams {
     const int* num_splits;    // [b+1]
     float* o_accum;           // [splits][s_q][64][512]
     float* lse_accum;         // [splits][s_q][64]
+    int page_shift, extra_page_shift;         // log2(page size) when it is a power of two, else -1
     long long pool_rows, extra_pool_rows;     // decode: keys in each pool (num_blocks * page_size); indices beyond are skipped
     unsigned long long* prof; // profiling builds: [2 CTAs][64] stall cycles of cluster 0, else null
 };
@@ -151,22 +157,21 @@ struct __align__(1024) SmemPlan {
     uint8_t k[kKStages][4 * 64 * 128];             // [chunk][key of this CTA][128 B]
     uint8_t v[kVStages][2 * 128 * 128];            // [chunk of this CTA][key][128 B]
     uint8_t s[2][64 * 128];                        // [row][128 keys], 128-byte swizzle
-    __align__(16) uint2 kslot[kKStages][kTileKeys]; // scale bytes 0-7 of every key of the tile, as gathered (K ring)
     __align__(16) uint16_t kvalid[kKStages][8];     // validity bits of the tile's keys, 16 per entry (K ring)
     __align__(128) uint32_t q_sf[64 * 4];          // scale rows for tcgen05.cp (64 rows x 16 B)
-    __align__(128) uint32_t k_sf[kKStages][64 * 4];   // per K stage: written when the stage has landed, read by that tile's QK
+    __align__(128) uint32_t k_sf[kKStages][64 * 4];   // per K stage: K scale rows for tcgen05.cp, gathered by the producers with the rows
     __align__(128) uint32_t s_sf[2][64 * 4];
     __align__(16) float tok_scale[kScStages][kTileKeys];
     __align__(16) uint32_t valid[kScStages][4];
-    float xmax[2][2][128];                         // [group][tile parity][lane]: row max of the lane's 64 keys
-    float m_pub[2][64];                            // [group][row]: running max after the group's latest tile
-    float xl[256], xr[256];                        // [group*128 + lane]: partial l and true max at the end of a pair
+    float xmax[kMaxGroups][2][128];                   // [group][parity of the group's tile count][lane]: row max of the lane's 64 keys
+    float m_pub[kMaxGroups][64];                      // [group][row]: running max after the group's latest tile
+    float xl[kMaxGroups * 128], xr[kMaxGroups * 128];    // [group*128 + lane]: partial l and true max at the end of a pair
     uint64_t bar_q_landed;                         // local: Q bytes landed
     uint64_t bar_q_full;                           // CTA0: Q data + scale rows of both CTAs ready
     uint64_t bar_q_empty;                          // both: every QK of the pair finished (2 arrivals)
     uint64_t bar_k_landed[kKStages];               // local: this CTA's K rows landed (128 arrivals)
-    uint64_t bar_k_full[kKStages];                 // CTA0: CTA1's K rows landed
-    uint64_t bar_v_full[kVStages];                 // CTA0: V rows of both CTAs landed (8 arrivals + 64 KB of TMA bytes)
+    uint64_t bar_v_landed[kVStages];               // local: this CTA's cp.async half of the V rows landed (128 arrivals)
+    uint64_t bar_v_full[kVStages];                 // CTA0: gather4 halves of both CTAs landed (8 arrivals + bytes), and CTA 1's cp.async half (1)
     uint64_t bar_qk_done[kScStages];               // both: QK of tile g finished (ring by g % 4)
     uint64_t bar_pv_done[kScStages];               // both: PV of tile g finished
     uint64_t bar_pv_half[2];                       // both: first key half accumulated (64-key tiles)
@@ -176,13 +181,12 @@ struct __align__(1024) SmemPlan {
     uint64_t bar_p_empty[2];                       // CTA0: P buffer copied to registers
     uint64_t bar_s_full[2][2];                     // CTA0: [buffer][key half]
     uint64_t bar_o_empty;                          // CTA0: epilogue has drained O
-    uint64_t bar_m_ready[2];                       // local: group g published the running max of its tile
+    uint64_t bar_m_ready[kMaxGroups];                 // local: group g published the running max of its tile
     uint32_t tmem_base;
     int abort_word;
     DeviceFault* fault;                            // copy of the kernel parameter, for the out-of-line wait path
 #ifdef MXDSA_PROFILE
     unsigned long long prof[64];
-    int ev[16][24];
 #endif
 };
 
@@ -308,7 +312,9 @@ __device__ __forceinline__ const uint8_t* key_resolve(const AttnParams& p, const
         valid = idx >= 0 && idx < (extra ? p.extra_pool_rows : p.pool_rows) && pos < (extra ? w.elen : w.len);
         if (!valid) return nullptr;
         const unsigned psz = extra ? p.extra_page_size : p.page_size;
-        const unsigned page = (unsigned)idx / psz, in_page = (unsigned)idx % psz;
+        const int sh = extra ? p.extra_page_shift : p.page_shift;   // pages are powers of two as a rule: no division then
+        const unsigned page = sh >= 0 ? (unsigned)idx >> sh : (unsigned)idx / psz;
+        const unsigned in_page = sh >= 0 ? (unsigned)idx & (psz - 1) : (unsigned)idx % psz;
         const uint8_t* pg = (extra ? p.extra_kv : p.kv) + (long long)page * (extra ? p.extra_stride_block : p.stride_block);
         slot = pg + (long long)psz * kDim + (long long)in_page * 16;
         return pg + (long long)in_page * kDim;
@@ -364,13 +370,17 @@ __device__ __forceinline__ const void* key_rows4(const AttnParams& p, const Tens
         const int len = extra ? w.elen : w.len;
         const unsigned psz = extra ? p.extra_page_size : p.page_size;
         const unsigned rpb = extra ? p.extra_rows_per_block : p.rows_per_block;
+        const int sh = extra ? p.extra_page_shift : p.page_shift;
         const long long pool = extra ? p.extra_pool_rows : p.pool_rows;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const bool ok = blk < w.blk_end && id[i] >= 0 && id[i] < pool && pos + i < len;
-            r[i] = ok ? (int)(((unsigned)id[i] / psz) * rpb + (unsigned)id[i] % psz) : -1;
+            const unsigned page = sh >= 0 ? (unsigned)id[i] >> sh : (unsigned)id[i] / psz;
+            const unsigned in_page = sh >= 0 ? (unsigned)id[i] & (psz - 1) : (unsigned)id[i] % psz;
+            r[i] = ok ? (int)(page * rpb + in_page) : -1;
         }
-        return extra ? &maps.ekv : &maps.kv;
+        // without an extra pool there is no second map: positions past the main list have no row anyway
+        return (extra && p.extra_topk > 0) ? &maps.ekv : &maps.kv;
     }
 }
 
@@ -406,6 +416,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, uint32_t bytes) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
 // one arrival on `bar` once all cp.async issued so far by this thread have landed
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
@@ -419,7 +432,6 @@ template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
 
 // multiply the 256 O columns of this thread's tensor-memory lane by f (out of line: one copy)
 __device__ __noinline__ void rescale_o(uint32_t lane_addr, float f) {
-#ifdef MXDSA_RESCALE_WIDE
     // 64 columns per round: half as many exposed load latencies
 #pragma unroll 1
     for (int c = 0; c < 256; c += 64) {
@@ -432,17 +444,6 @@ __device__ __noinline__ void rescale_o(uint32_t lane_addr, float f) {
         tmem_st32(lane_addr + kColO + c, v);
         tmem_st32(lane_addr + kColO + c + 32, v + 32);
     }
-#else
-#pragma unroll 1
-    for (int c = 0; c < 256; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(lane_addr + kColO + c, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-        tmem_st32(lane_addr + kColO + c, v);
-    }
-#endif
     tmem_wait_st();
 }
 // one 32-byte store (a whole sector); the address must be 32-byte aligned
@@ -456,6 +457,10 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 }
 
 #ifdef MXDSA_PROFILE
+#ifndef MXDSA_EV_CTA
+#define MXDSA_EV_CTA 0
+#endif
+#define MXDSA_EV_STORE(gtile, id) { if (blockIdx.x == MXDSA_EV_CTA && blockIdx.y == 0 && p.prof != nullptr) p.prof[128 + ((gtile)-16) * 24 + (id)] = (unsigned long long)(clock64() - prof_kernel_t0); }
 // per-wait stall accounting (cycles spent in each numbered wait, summed over the lanes' leader)
 #ifdef MXDSA_PROFILE_LIGHT   // event stamps only, and only those of MXDSA_EV_MASK: perturbs the timeline far less
 #define MXDSA_PROF_BEGIN
@@ -473,16 +478,16 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 #define MXDSA_EV(gtile, id)
 #define MXDSA_EVW2(gtile, id)
 #define MXDSA_EVW(gtile, id) \
-    if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
+    if ((gtile) >= 16 && (gtile) < 32) MXDSA_EV_STORE(gtile, id)
 #else
 #define MXDSA_EVW(gtile, id)
 #ifdef MXDSA_X_QKEV
-#define MXDSA_EVW2(gtile, id) if ((gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
+#define MXDSA_EVW2(gtile, id) if ((gtile) >= 16 && (gtile) < 32) MXDSA_EV_STORE(gtile, id)
 #else
 #define MXDSA_EVW2(gtile, id)
 #endif
 #define MXDSA_EV(gtile, id) \
-    if ((((MXDSA_EV_MASK) >> (id)) & 1u) && (gtile) >= 16 && (gtile) < 32) sm.ev[(gtile)-16][(id)] = (int)(clock64() - prof_kernel_t0);
+    if ((((MXDSA_EV_MASK) >> (id)) & 1u) && (gtile) >= 16 && (gtile) < 32) MXDSA_EV_STORE(gtile, id)
 #endif
 #else
 #define MXDSA_EVW(gtile, id)
@@ -548,8 +553,8 @@ __device__ __noinline__ void raise_fault(SmemPlan& sm, int code) {
     if (atomicCAS(&sm.fault->flag, 0, 1) == 0) sm.fault->where = code;
 }
 
-template <bool DECODE, int NT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool DECODE, int NT, int G>
+__global__ void __launch_bounds__(kBaseThreads + 128 * G, 1)
 mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ TensorMaps maps) {
     extern __shared__ uint8_t smem_raw[];
     // The plan starts at the first 1024-byte boundary.  The pointer is formed by adding an offset to
@@ -567,10 +572,14 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         mbar_init(smem_u32(&sm.bar_q_empty), 2);
         for (int i = 0; i < kKStages; ++i) {
             mbar_init(smem_u32(&sm.bar_k_landed[i]), 128 + 4);   // 128 copy completions + one plain arrival per producer warp
-            mbar_init(smem_u32(&sm.bar_k_full[i]), 1);
         }
         for (int i = 0; i < kVStages; ++i) {
+#ifndef MXDSA_V_SPLIT
             mbar_init(smem_u32(&sm.bar_v_full[i]), 8);
+#else
+            mbar_init(smem_u32(&sm.bar_v_full[i]), 9);
+#endif
+            mbar_init(smem_u32(&sm.bar_v_landed[i]), 128);
         }
         for (int i = 0; i < kScStages; ++i) {
             mbar_init(smem_u32(&sm.bar_qk_done[i]), 1);
@@ -586,8 +595,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             mbar_init(smem_u32(&sm.bar_pv_half[i]), 1);
         }
         mbar_init(smem_u32(&sm.bar_o_empty), 16);
-        mbar_init(smem_u32(&sm.bar_m_ready[0]), 4);
-        mbar_init(smem_u32(&sm.bar_m_ready[1]), 4);
+        for (int i = 0; i < kMaxGroups; ++i) mbar_init(smem_u32(&sm.bar_m_ready[i]), 4);
         sm.abort_word = 0;
         sm.fault = p.fault;
 #ifdef MXDSA_PROFILE
@@ -631,30 +639,31 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     const uint64_t desc_sf = smem_desc_base(0, 128, 0);       // scale rows, 16 bytes each
 
     // ------------------------------------------------------------------ roles
-    // Register budget: the launch gives every thread 96 (640 x 96 = 61440, and that -- not the SM's
-    // whole file -- is the pool setmaxnreg draws from; an increase beyond it would block for ever).
-    // The copy and control warps hand most of theirs back so that the softmax warps (64 logits per
-    // thread in registers) can work without spilling: 8 x 32 x 56 + 4 x 32 x 64 + 8 x 32 x 152 = 61440.
+    // Register budget.  The launch gives every thread kLaunchRegs (the most that 640 or 768 threads can have),
+    // and that allocation -- not the SM's whole file -- is the pool setmaxnreg draws from: an increase beyond
+    // what the other warps have released would block for ever, hence the static_assert, and the host refuses
+    // to launch unless the compiled kernel really has kLaunchRegs registers.  The copy and control warps hand
+    // most of theirs back so that the softmax warps (64 logits per thread in registers) work without spilling.
     // Each setmaxnreg is executed by the four warps of one aligned warp group with the same value.
-    // Measured: prefill gains 8%, decode (short work items, heavier address arithmetic in the copy
-    // warps) loses 15%, so only prefill rebalances.
+    constexpr int kGroups = G;
+    constexpr int kThreads = kBaseThreads + 128 * G;
+    constexpr int kLaunchRegs = launch_regs(G);
 #ifdef MXDSA_X_REBAL_ALL
     constexpr bool kRebalanceRegs = true;
 #else
-    constexpr bool kRebalanceRegs = !DECODE;
+    constexpr bool kRebalanceRegs = G == 3 || !DECODE;
 #endif
-    constexpr int kRegsCopy = MXDSA_REGS_COPY, kRegsCtl = MXDSA_REGS_CTL;
-    constexpr int kRegsSoftmax = (kThreads * 96 - 8 * 32 * kRegsCopy - 4 * 32 * kRegsCtl) / (8 * 32);
-    static_assert(kRegsSoftmax % 8 == 0 && 8 * 32 * kRegsCopy + 4 * 32 * kRegsCtl + 8 * 32 * kRegsSoftmax == kThreads * 96,
-                  "register budget must add up to the launch allocation exactly");
+    constexpr int kRegsCopy = 64, kRegsGather = G == 2 ? 64 : 40, kRegsCtl = 64, kRegsSoftmax = G == 2 ? 144 : 104;
+    static_assert(4 * 32 * (kRegsCopy + kRegsGather + kRegsCtl) + 4 * G * 32 * kRegsSoftmax <= kThreads * kLaunchRegs,
+                  "register budget must fit in the launch allocation");
     if (warp < 8) {
-        if constexpr (kRebalanceRegs) setmaxnreg_dec<kRegsCopy>();
         if (warp < 4) {
+            if constexpr (kRebalanceRegs) setmaxnreg_dec<kRegsCopy>();
             // ===================== K producers (warps 0-3): 16-byte cp.async =====================
             // Warp pw copies rows 64*cta + 16*pw + i (i < 16) of every tile, whole 512-byte rows, one row per
             // instruction: lane L writes byte chunk L of the row -> chunk tile L/8, 16-byte column (L%8) ^ (row%8).
             // It also gathers the 8 scale bytes of 32 keys of the tile (its own 16 and the matching 16 of the
-            // peer CTA's half) into sm.kslot: every CTA needs the scales of all 128 keys.
+            // peer CTA's half) into sm.k_sf: every CTA needs the scales of all 128 keys.
             // Raw indices are loaded one tile ahead and turned into addresses only when the tile is copied: a warp
             // issues in order, so an address computed at load time would hold the warp until the load is back.
             const int pw = warp;
@@ -690,7 +699,13 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const int r = 16 * pw + i;
                     cp_async16(base + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src ? src + lane * 16 : p.kv, src ? 16u : 0u);
                 }
-                cp_async8(smem_u32(&sm.kslot[s][key]), slot ? slot : p.kv, slot ? 8u : 0u);
+                // the key's 8 scale bytes go straight into the row layout that tcgen05.cp wants: row (key/64)*32 +
+                // key%32 holds {bytes0-3[k], bytes0-3[k+32], bytes4-7[k], bytes4-7[k+32]} of keys k and k+32
+                {
+                    const uint32_t dst = smem_u32(&sm.k_sf[s][((key >> 6) * 32 + (key & 31)) * 4 + ((key >> 5) & 1)]);
+                    cp_async4(dst, slot ? slot : p.kv, slot ? 4u : 0u);
+                    cp_async4(dst + 8, slot ? slot + 4 : p.kv, slot ? 4u : 0u);
+                }
                 cp_async_arrive(smem_u32(&sm.bar_k_landed[s]));
                 if (lane == 0) {   // validity of the warp's 32 keys: a plain store, released by a plain arrival
                     sm.kvalid[s][4 * cta + pw] = (uint16_t)vbits;
@@ -701,6 +716,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 ++kt;
             }
         } else {
+            if constexpr (kRebalanceRegs) setmaxnreg_dec<kRegsGather>();
             // ===================== V producers (warps 4-7): TMA gather4 =====================
             // CTA c stages bytes 256c .. 256c+255 of all 128 keys of a tile as [chunk of 128 B][key][128 B].
             // Warp pw takes keys 32*pw .. 32*pw+31; its lanes 0-7 own four keys each and issue two gather4
@@ -729,14 +745,41 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 const void* map = key_rows4<DECODE>(p, maps, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64, ix, r);
                 cv.advance();
                 if (cv.live) ix = key_index4<DECODE>(p, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64);
+#ifndef MXDSA_V_SPLIT
                 if (lane == 0) mbar_expect_tx_cluster(v_full0 + s * 8, 2 * 32 * 128);
                 __syncwarp();
                 if (lane < 8) {
                     const uint32_t dst = v_dst0 + s * 32768;
-                    tma_gather4_pair(dst, map, 256 * (int)cta, r[0], r[1], r[2], r[3], v_full0 + s * 8, kEvictLast);
-                    tma_gather4_pair(dst + 16384, map, 256 * (int)cta + 128, r[0], r[1], r[2], r[3], v_full0 + s * 8, kEvictLast);
+                    tma_gather4_pair(dst, map, 256 * (int)cta, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
+                    tma_gather4_pair(dst + 16384, map, 256 * (int)cta + 128, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
                 }
                 __syncwarp();
+#else
+                // The copy engine alone needs longer for a tile's 32 KB than the tile should take, and so would
+                // the cp.async path if it carried V on top of K: chunk 0 goes by gather4, chunk 1 by cp.async.
+                if (lane == 0) mbar_expect_tx_cluster(v_full0 + s * 8, 32 * 128);
+                __syncwarp();
+                if (lane < 8)
+                    tma_gather4_pair(v_dst0 + s * 32768, map, 256 * (int)cta, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
+                __syncwarp();
+                {
+                    // a row coordinate r of the 2-D view is byte offset 512 r of the store
+                    const uint8_t* base = (DECODE && map == static_cast<const void*>(&maps.ekv)) ? p.extra_kv : p.kv;
+                    const uint32_t dst1 = smem_u32(sm.v[0]) + s * 32768 + 16384;
+#pragma unroll 2
+                    for (int i = 0; i < 8; ++i) {   // instruction i: keys 4i .. 4i+3 of this warp's 32 (owned by lane i), 128 bytes each
+                        const int c0 = __shfl_sync(0xffffffffu, r[0], i), c1 = __shfl_sync(0xffffffffu, r[1], i);
+                        const int c2 = __shfl_sync(0xffffffffu, r[2], i), c3 = __shfl_sync(0xffffffffu, r[3], i);
+                        const int sub = lane >> 3;
+                        const int rr = sub == 0 ? c0 : sub == 1 ? c1 : sub == 2 ? c2 : c3;
+                        const int k = 32 * pw + 4 * i + sub;
+                        cp_async16(dst1 + k * 128 + (((lane & 7) ^ (k & 7)) << 4),
+                                   rr >= 0 ? base + (long long)rr * 512 + 256 * (int)cta + 128 + (lane & 7) * 16 : p.kv,
+                                   rr >= 0 ? 16u : 0u);
+                    }
+                    cp_async_arrive(smem_u32(&sm.bar_v_landed[s]));
+                }
+#endif
                 if (pw == 0 && lane == 0) { MXDSA_EV(vt, 3) }
                 ++vt;
             }
@@ -770,17 +813,16 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #pragma unroll 1
                 for (int t = 0; t < ntiles; ++t, ++gt) {
                     if ((gt & 1) != e) continue;
-                    const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
+                    const uint32_t s = gt % kKStages;
                     const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                     const uint32_t bph = (gt >> 1) & 1;
                     MXDSA_WAIT_TIGHT(sm.bar_sc_full[sc], sph, 21);
                     MXDSA_EVW2(gt, 16)
                     MXDSA_WAIT_TIGHT(sm.bar_p_empty[e], bph ^ 1, 22);
                     MXDSA_EVW2(gt, 17)
-                    MXDSA_WAIT_TIGHT(sm.bar_k_landed[s], ph, 23);
-                    MXDSA_EVW2(gt, 18)
-                    MXDSA_WAIT_TIGHT(sm.bar_k_full[s], ph, 24);
-                    fence_proxy_async_smem();   // rows written by cp.async are read by the tensor core
+                    // "scale rows ready" comes from the stagers of both CTAs, each of which has seen its CTA's K rows
+                    // land and has fenced them towards the tensor core: nothing else to wait for
+                    fence_proxy_async_smem();
                     MXDSA_EV(gt, 6)
                     tc_fence_after();
                     __syncwarp();
@@ -818,24 +860,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 __syncwarp();
                 ++gw;
             }
-        } else if (cta == 1 && warp == 8 && lane == 0) {
-            // ===================== K relay (CTA 1) =====================
-            WorkIter<DECODE> it(p);
-            WorkItem w;
-            uint32_t gt = 0;
-            const uint32_t k_full0 = map_to_cta(smem_u32(&sm.bar_k_full[0]), 0);
-#pragma unroll 1
-            while (it.template next<NT>(w)) {
-                const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
-                if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-#pragma unroll 1
-                for (int t = 0; t < ntiles; ++t, ++gt) {
-                    const uint32_t s = gt % kKStages, ph = (gt / kKStages) & 1;
-                    MXDSA_WAIT_TIGHT(sm.bar_k_landed[s], ph, 12);
-                    fence_proxy_async_smem();
-                    mbar_arrive_cluster(k_full0 + s * 8);
-                }
-            }
         }
     } else if (warp == 10) {
         if (cta == 0) {
@@ -857,6 +881,10 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const uint32_t b = gt & 1, bph = (gt >> 1) & 1;
                     const uint32_t sc = gt % kScStages;
                     MXDSA_WAIT_TIGHT(sm.bar_v_full[s], ph, 34);
+#ifdef MXDSA_V_SPLIT
+                    MXDSA_WAIT_TIGHT(sm.bar_v_landed[s], ph, 31);
+                    fence_proxy_async_smem();   // rows written by cp.async are read by the tensor core
+#endif
                     const uint64_t a_base = smem_desc(desc_k128, smem_u32(sm.s[b]));
                     const uint64_t b_base = smem_desc(desc_v, smem_u32(sm.v[s]));
                     const uint32_t sfa = tmem + kColSs + 4 * b;
@@ -893,6 +921,26 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 }
                 ++gw;
             }
+#ifdef MXDSA_V_SPLIT
+        } else if (lane == 0) {
+            // ===================== V relay (CTA 1): tells CTA 0 that this CTA's cp.async half has landed =====
+            WorkIter<DECODE> it(p);
+            WorkItem w;
+            uint32_t gt = 0;
+            const uint32_t v_full0 = map_to_cta(smem_u32(&sm.bar_v_full[0]), 0);
+#pragma unroll 1
+            while (it.template next<NT>(w)) {
+                const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
+                if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+#pragma unroll 1
+                for (int t = 0; t < ntiles; ++t, ++gt) {
+                    const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
+                    MXDSA_WAIT_THREAD(sm.bar_v_landed[s], ph, 13);
+                    fence_proxy_async_smem();
+                    mbar_arrive_cluster(v_full0 + s * 8);
+                }
+            }
+#endif
         }
     } else if (warp == 11) {
         // ===================== operand stager =====================
@@ -907,6 +955,17 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
             // ---- Q tile and Q scale rows of this CTA's token
             const int tok = min(2 * w.pair + (int)cta, p.s_q - 1);
+            if (lane == 0) {   // ask for the NEXT work item's Q tile to be brought into L2 while this one is worked on
+                WorkIter<DECODE> peek = it;
+                WorkItem wn;
+                if (peek.template next<NT>(wn)) {
+                    const int tokn = min(2 * wn.pair + (int)cta, p.s_q - 1);
+                    asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];" ::"l"(&maps.q),
+                                 "r"(0), "r"(0), "r"(0), "r"(tokn), "r"(wn.req)
+                                 : "memory");
+                }
+            }
+            __syncwarp();
             MXDSA_WAIT(sm.bar_q_empty, (gw & 1) ^ 1, 40);
             if (lane == 0) {
                 mbar_expect_tx(smem_u32(&sm.bar_q_landed), 4 * 64 * 128);
@@ -939,24 +998,22 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 MXDSA_EV(gt, 13)
                 MXDSA_WAIT_TIGHT(sm.bar_k_landed[ks], (gt / kKStages) & 1, 44);
                 MXDSA_EV(gt, 5)
-                uint2 sv[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) sv[j] = sm.kslot[ks][j * 32 + lane];
-                const uint32_t vword = reinterpret_cast<const uint32_t*>(sm.kvalid[ks])[lane & 3];
-                // rows for tcgen05.cp: row r = (half of the tile)*32 + L holds keys (half*64 + L) and (+32):
-                // {bytes0-3[k0], bytes0-3[k1], bytes4-7[k0], bytes4-7[k1]}.  The rows of K stage ks were last read
-                // by the QK of tile gt-2, which finished before the stage was refilled.
-                *reinterpret_cast<uint4*>(&sm.k_sf[ks][lane * 4]) = make_uint4(sv[0].x, sv[1].x, sv[0].y, sv[1].y);
-                *reinterpret_cast<uint4*>(&sm.k_sf[ks][(32 + lane) * 4]) = make_uint4(sv[2].x, sv[3].x, sv[2].y, sv[3].y);
+                // The K rows, the scale rows and the validity bits of this CTA have landed.  Publish at once (the
+                // fence makes what cp.async wrote visible to the tensor core), then derive what the softmax reads.
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(sc_full0 + sc * 8);
                 MXDSA_EV(gt, 4)
-                // what the softmax warps read: ring of 4, a stage is free once the softmax of tile gt-4 is through
+                // token scale = 2^(scale byte 0 - 127); keys L, L+32 sit in words 0, 1 of row L, keys L+64, L+96 in row 32+L
+                const uint2 lo = *reinterpret_cast<const uint2*>(&sm.k_sf[ks][lane * 4]);
+                const uint2 hi = *reinterpret_cast<const uint2*>(&sm.k_sf[ks][(32 + lane) * 4]);
+                const uint32_t vword = reinterpret_cast<const uint32_t*>(sm.kvalid[ks])[lane & 3];
+                // ring of 4: a stage is free once the softmax of tile gt-4 is through
                 if (gt >= kScStages) MXDSA_WAIT(sm.bar_tok_empty[sc], sph ^ 1, 43);
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    sm.tok_scale[sc][j * 32 + lane] = __uint_as_float((sv[j].x & 0xffu) << 23);
+                sm.tok_scale[sc][lane] = __uint_as_float((lo.x & 0xffu) << 23);
+                sm.tok_scale[sc][32 + lane] = __uint_as_float((lo.y & 0xffu) << 23);
+                sm.tok_scale[sc][64 + lane] = __uint_as_float((hi.x & 0xffu) << 23);
+                sm.tok_scale[sc][96 + lane] = __uint_as_float((hi.y & 0xffu) << 23);
                 if (lane < 4) sm.valid[sc][lane] = vword;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&sm.bar_tok_full[sc]));
@@ -971,13 +1028,14 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     }
     } else {
         if constexpr (kRebalanceRegs) setmaxnreg_inc<kRegsSoftmax>();
-        // ===================== softmax + epilogue (warps 12-19) =====================
+        // ===================== softmax + epilogue (warps 12 ..) =====================
         // Two groups of four warps take alternate tiles (group = tile parity = P buffer), so one
         // group's exp / quantise / store phase overlaps the other group's load / max phase.  Inside a
         // group a thread owns one row and one 64-key half of the tile (two UE8M0 scale groups of S).
         // The only serial link between consecutive tiles is the running maximum: after deciding m_t a
         // group publishes it (sm.m_pub) and the other group picks it up before deciding m_{t+1}.
         const int grp = (warp - 12) >> 2;
+        const int prev_grp = (grp + kGroups - 1) % kGroups;
         const int q4 = warp & 3;                 // lane quadrant of tensor memory
         const int L = q4 * 32 + lane;            // tensor-memory lane
         const int row = L % 64;                  // head
@@ -998,9 +1056,9 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             float l = 0.f, real_m = -CUDART_INF_F;
 #pragma unroll 1
             for (int t = 0; t < ntiles; ++t, ++gt) {
-                if ((int)(gt & 1) != grp) continue;
+                if ((int)(gt % kGroups) != grp) continue;
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
-                const uint32_t b = grp, bph = (gt >> 1) & 1;
+                const uint32_t b = gt & 1, bph = (gt >> 1) & 1;   // P and S buffer of the tile and the phase of their barriers
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 22) }
                 MXDSA_WAIT_POLL(sm.bar_tok_full[sc], sph, 50);
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 23) }
@@ -1029,7 +1087,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     for (int j = 0; j < 8; ++j) mx8[j] = fmax3(mx8[j], x[i + j], x[i + 8 + j < 64 ? i + 8 + j : i + j]);
                 }
                 const float own_max = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * p.scale_log2;
-                float* xm = sm.xmax[grp][bph];
+                float* xm = sm.xmax[grp][(gt / kGroups) & 1];
                 xm[L] = own_max;
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 16) }
                 named_bar_sync(1 + grp, 128);
@@ -1037,8 +1095,8 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 const float peer_max = xm[L ^ 64];
                 // the running maximum handed over by the other group (value ignored on a pair's first
                 // tile, but every phase of that barrier is observed)
-                if (gt > 0) MXDSA_WAIT_POLL(sm.bar_m_ready[grp ^ 1], ((gt - 1) >> 1) & 1, 58);
-                const float m_prev = t == 0 ? -1e30f : sm.m_pub[grp ^ 1][row];
+                if (gt > 0) MXDSA_WAIT_POLL(sm.bar_m_ready[prev_grp], ((gt - 1) / kGroups) & 1, 58);
+                const float m_prev = t == 0 ? -1e30f : sm.m_pub[prev_grp][row];
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 10) }
                 const float sprev = (m_own == m_prev) ? 1.f : ex2_approx(m_own - m_prev);
                 // numerical tiles: NT = 128 -> one per tensor-core tile; NT = 64 -> key half 0 then 1
@@ -1074,15 +1132,12 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     MXDSA_WAIT_POLL(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 52);
                 }
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 19) }
-                // probabilities, key-scaled, re-quantised per 32 keys and stored.  The two 32-key blocks
-                // run through ONE copy of the code (the second block's logits are moved down into the
-                // first block's registers): the instruction cache, not the register file, is scarce.
+                // probabilities, key-scaled, re-quantised per 32 keys and stored
                 const float2 negm2 = make_float2(-m_used, -m_used);
                 const float4* tok4 = reinterpret_cast<const float4*>(&sm.tok_scale[sc][half * 64]);
                 uint8_t* srow = sm.s[b];
                 float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
                 uint32_t e_bytes = 0;
-#ifdef MXDSA_EXP_UNROLLED
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
                     uint32_t s8[8];
@@ -1120,59 +1175,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + g * 32)) = make_uint4(s8[0], s8[1], s8[2], s8[3]);
                     *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + g * 32 + 16)) = make_uint4(s8[4], s8[5], s8[6], s8[7]);
                 }
-#else
-#pragma unroll 1
-                for (int g = 0; g < 2; ++g) {
-                    uint32_t s8[8];
-                    uint32_t e;
-                    {
-                        float am = 0.f;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-#ifdef MXDSA_X_NOTOK
-                            const float4 tk = make_float4(1.f, 1.f, 1.f, 1.f);
-#else
-                            const float4 tk = tok4[g * 8 + i / 4];
-#endif
-                            float2 a = f2_fma(make_float2(x[i], x[i + 1]), scale2, negm2);
-                            float2 c = f2_fma(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
-#ifndef MXDSA_X_NOEX2
-                            a = make_float2(ex2_approx(a.x), ex2_approx(a.y));
-                            c = make_float2(ex2_approx(c.x), ex2_approx(c.y));
-#endif
-                            sum2[0] = f2_add(sum2[0], a);
-                            sum2[1] = f2_add(sum2[1], c);
-                            a = f2_mul(a, make_float2(tk.x, tk.y));
-                            c = f2_mul(c, make_float2(tk.z, tk.w));
-                            am = fmax3(am, a.x, a.y);
-                            am = fmax3(am, c.x, c.y);
-                            x[i] = a.x; x[i + 1] = a.y; x[i + 2] = c.x; x[i + 3] = c.y;
-                        }
-                        e = cvt_ue8m0_roundup(am > 0.f ? __fdividef(am, 448.0f) : 1.0f);
-                        e = max(e, 61u);
-                        const float mulf = __uint_as_float((254u - e) << 23);
-                        const float2 mul2 = make_float2(mulf, mulf);
-                        if (g == 0 && warp == 12 && lane == 0) { MXDSA_EV(gt, 18) }
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const float2 a = f2_mul(make_float2(x[i], x[i + 1]), mul2);
-                            const float2 c = f2_mul(make_float2(x[i + 2], x[i + 3]), mul2);
-#ifdef MXDSA_X_NOCVT
-                            s8[i / 4] = __float_as_uint(a.x) ^ __float_as_uint(a.y) ^ __float_as_uint(c.x) ^ __float_as_uint(c.y);
-#else
-                            s8[i / 4] = (uint32_t)cvt_e4m3x2(a.x, a.y) | ((uint32_t)cvt_e4m3x2(c.x, c.y) << 16);
-#endif
-                        }
-                    }
-                    e_bytes |= e << (8 * g);
-                    *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + g * 32)) = make_uint4(s8[0], s8[1], s8[2], s8[3]);
-                    *reinterpret_cast<uint4*>(srow + swz128(row, half * 64 + g * 32 + 16)) = make_uint4(s8[4], s8[5], s8[6], s8[7]);
-                    if (g == 0) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) x[i] = x[32 + i];
-                    }
-                }
-#endif
                 // scale rows: row (row%32) and its copy at +32; word row/32; bytes 2*half, 2*half+1
                 reinterpret_cast<uint16_t*>(&sm.s_sf[b][(row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
                 reinterpret_cast<uint16_t*>(&sm.s_sf[b][(32 + row % 32) * 4 + row / 32])[half] = (uint16_t)e_bytes;
@@ -1221,19 +1223,31 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             // ---------------- end of the pair: final m, the four partial l of each row, drain O
             const uint32_t last = gt - 1;
             float m_fin = m_own;
-            if ((int)(last & 1) != grp) {
-                MXDSA_WAIT_POLL(sm.bar_m_ready[grp ^ 1], (last >> 1) & 1, 59);
-                m_fin = sm.m_pub[grp ^ 1][row];
+            const int last_grp = (int)(last % kGroups);
+            if (last_grp != grp) {
+                MXDSA_WAIT_POLL(sm.bar_m_ready[last_grp], (last / kGroups) & 1, 59);
+                m_fin = sm.m_pub[last_grp][row];
                 l *= (m_own == m_fin) ? 1.f : ex2_approx(m_own - m_fin);
             }
             sm.xl[grp * 128 + L] = l;
             sm.xr[grp * 128 + L] = real_m;
-            named_bar_sync(3, 256);
+            named_bar_sync(1 + kGroups, kGroups * 128);
             const float* xl = sm.xl;
             const float* xr = sm.xr;
             float l_tot = (xl[row] + xl[64 + row]) + (xl[128 + row] + xl[192 + row]);
-            const float real_all = fmaxf(fmaxf(xr[row], xr[64 + row]), fmaxf(xr[128 + row], xr[192 + row]));
-            named_bar_sync(3, 256);   // everybody has read the exchange area before the next pair writes it
+            float real_all = fmaxf(fmaxf(xr[row], xr[64 + row]), fmaxf(xr[128 + row], xr[192 + row]));
+            if constexpr (kGroups == 3) {
+                l_tot += xl[256 + row] + xl[320 + row];
+                real_all = fmaxf(real_all, fmaxf(xr[256 + row], xr[320 + row]));
+            }
+            named_bar_sync(1 + kGroups, kGroups * 128);   // everybody has read the exchange area before the next pair writes it
+            // Two groups drain O, 128 columns per thread; the group whose turn the next tile is goes straight on
+            // to the next pair, so that its softmax overlaps the drain.
+            const int drain = kGroups == 2 ? grp : (grp - (int)((last + 1) % kGroups) + kGroups) % kGroups - 1;   // -1: not draining
+            if (drain < 0) {
+                ++gw;
+                continue;
+            }
             float m = m_fin;
             if (real_all == -CUDART_INF_F) {
                 l_tot = 0.f;
@@ -1248,7 +1262,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             if (!DECODE || !w.split) oscale = __fdividef(1.0f, l_tot + ex2_approx(fmaf(sink, CUDART_L2E_F, -m)));
             else oscale = __fdividef(1.0f, l_tot);
             if (l_tot == 0.f) oscale = 0.f;
-            if (grp == 0 && half == 0 && store) {
+            if (drain == 0 && half == 0 && store) {
                 if (!DECODE || !w.split) {
                     float lse = fmaf(m, CUDART_LN2_F, CUDART_LN2_F * lg2_approx(l_tot));
                     if (l_tot == 0.f || lse == -CUDART_INF_F) lse = CUDART_INF_F;
@@ -1259,13 +1273,13 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     p.lse_accum[((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row] = lg2_approx(l_tot) + m;
                 }
             }
-            const int dim0 = half * 256 + grp * 128;   // this thread's 128 output dims
+            const int dim0 = half * 256 + drain * 128;   // this thread's 128 output dims
             if (!DECODE || !w.split) {
                 __nv_bfloat16* dst = p.out + (((long long)w.req * p.s_q + tok_idx) * kHeads + row) * kDim + dim0;
 #pragma unroll 1
                 for (int c = 0; c < 128; c += 32) {
                     float o[32];
-                    tmem_ld32(lane_addr + kColO + grp * 128 + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_ld32(lane_addr + kColO + drain * 128 + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
                         // 32 columns -> 64 bytes of bf16: two 32-byte stores per lane (whole sectors; sixteen-byte
@@ -1289,7 +1303,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #pragma unroll 1
                 for (int c = 0; c < 128; c += 32) {
                     float o[32];
-                    tmem_ld32(lane_addr + kColO + grp * 128 + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_ld32(lane_addr + kColO + drain * 128 + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
@@ -1318,7 +1332,7 @@ done:
     // follow).  In a normal exit the arrivals are harmless: nobody waits on that barrier any more.
     if (warp >= 12) {
         named_bar_arrive(1 + ((warp - 12) >> 2), 128);
-        named_bar_arrive(3, 256);
+        named_bar_arrive(1 + kGroups, kGroups * 128);
     }
     tc_fence_before();
     __syncthreads();
@@ -1326,11 +1340,6 @@ done:
     if (p.prof != nullptr && blockIdx.x < 2 && blockIdx.y == 0 && threadIdx.x < 64) {
         if (threadIdx.x == 0) sm.prof[0] = (unsigned long long)(clock64() - prof_kernel_t0);
         p.prof[blockIdx.x * 64 + threadIdx.x] = sm.prof[threadIdx.x];
-#ifndef MXDSA_EV_CTA
-#define MXDSA_EV_CTA 0
-#endif
-        if (blockIdx.x == MXDSA_EV_CTA)
-            for (int i = threadIdx.x; i < 384; i += 64) p.prof[128 + i] = (unsigned long long)(unsigned)(&sm.ev[0][0])[i];
     }
 #endif
     cluster_sync();

@@ -99,9 +99,12 @@ int make_kv_map(CUtensorMap* map, const void* base, uint64_t rows) {
     cuuint64_t strides[1] = {512};
     cuuint32_t box[2] = {128, 1};
     cuuint32_t es[2] = {1, 1};
+#ifndef MXDSA_KV_PROMO
+#define MXDSA_KV_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+#endif
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, es,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          MXDSA_KV_PROMO, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         tl_last_cuda_error = (int)r;
         return MXDSA_ERR_CUDA;
@@ -111,13 +114,29 @@ int make_kv_map(CUtensorMap* map, const void* base, uint64_t rows) {
 
 constexpr size_t kSmemBytes = sizeof(mxdsa::SmemPlan) + 1024;
 
+#ifndef MXDSA_GROUPS_PREFILL
+#define MXDSA_GROUPS_PREFILL 3
+#endif
+#ifndef MXDSA_GROUPS_DECODE
+#define MXDSA_GROUPS_DECODE 3
+#endif
+
+// `groups` = softmax groups of the instantiation (the template's G): it fixes the block size and the register
+// allocation that the kernel's setmaxnreg budget assumes.
 template <typename K>
-int launch_pairs(K kernel, dim3 grid, cudaStream_t stream, const mxdsa::AttnParams& ap, const mxdsa::TensorMaps& maps) {
+int launch_pairs(K kernel, int groups, dim3 grid, cudaStream_t stream, const mxdsa::AttnParams& ap,
+                 const mxdsa::TensorMaps& maps) {
     static_assert(kSmemBytes <= 227 * 1024, "shared-memory plan exceeds the 227 KB per-CTA limit");
+    // The kernel re-balances registers between its roles against a pool of launch_regs(groups) per thread.
+    // If this build of the kernel was given a different number (another toolkit or flag set), an increase
+    // beyond the pool would block in hardware for ever: refuse to launch instead.
+    cudaFuncAttributes fa;
+    MX_CUDA(cudaFuncGetAttributes(&fa, kernel));
+    if (fa.numRegs != mxdsa::launch_regs(groups)) return MXDSA_ERR_DEVICE;
     MX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(mxdsa::kThreads);
+    cfg.blockDim = dim3(mxdsa::kBaseThreads + 128 * groups);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr{};
@@ -365,8 +384,9 @@ int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     const int clusters = ap.num_pairs < d->sm_count / 2 ? ap.num_pairs : d->sm_count / 2;
     const dim3 grid(2 * clusters, 1, 1);
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
-    if (p->topk >= 512) return launch_pairs(mxdsa::mxdsa_attn_kernel<false, 128>, grid, stream, ap, maps);
-    return launch_pairs(mxdsa::mxdsa_attn_kernel<false, 64>, grid, stream, ap, maps);
+    constexpr int G = MXDSA_GROUPS_PREFILL;
+    if (p->topk >= 512) return launch_pairs(mxdsa::mxdsa_attn_kernel<false, 128, G>, G, grid, stream, ap, maps);
+    return launch_pairs(mxdsa::mxdsa_attn_kernel<false, 64, G>, G, grid, stream, ap, maps);
 }
 
 int mxdsa_num_sm_parts(int device, int s_q) {
@@ -459,6 +479,9 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
         ap.eidx_stride_b = p->stride_extra_indices_b;
         ap.extra_topk_length = p->extra_topk_length;
     }
+    auto log2_exact = [](int v) { int s = 0; while ((1 << s) < v) ++s; return (1 << s) == v ? s : -1; };
+    ap.page_shift = log2_exact(p->page_block_size);
+    ap.extra_page_shift = has_extra ? log2_exact(p->extra_page_block_size) : -1;
     ap.pool_rows = (long long)p->num_blocks * p->page_block_size;
     ap.extra_pool_rows = has_extra ? (long long)p->extra_num_blocks * p->extra_page_block_size : 0;
     ap.sched_meta = p->sched_meta;
@@ -483,7 +506,7 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
 
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
     const dim3 grid(2 * ((p->s_q + 1) / 2), p->num_sm_parts, 1);
-    st = launch_pairs(mxdsa::mxdsa_attn_kernel<true, 64>, grid, stream, ap, maps);
+    st = launch_pairs(mxdsa::mxdsa_attn_kernel<true, 64, MXDSA_GROUPS_DECODE>, MXDSA_GROUPS_DECODE, grid, stream, ap, maps);
     if (st != MXDSA_OK) return st;
     const dim3 cgrid(p->num_sm_parts * p->s_q, MXDSA_HEADS / 8, 1);
     mxdsa_combine_kernel<<<cgrid, 256, 0, stream>>>(p->b, p->s_q, p->num_sm_parts, p->sched_meta, p->num_splits,
