@@ -58,8 +58,11 @@
 #define MXDSA_V_HINT kEvictLast
 #endif
 #ifndef MXDSA_K_STAGES
-#define MXDSA_K_STAGES 3
+#define MXDSA_K_STAGES 2
 #define MXDSA_V_STAGES 2
+#endif
+#ifndef MXDSA_S_BUFS
+#define MXDSA_S_BUFS 3
 #endif
 
 namespace mxdsa {
@@ -72,11 +75,12 @@ static constexpr int kRowBytes = 528;
 static constexpr int kTileKeys = 128;    // keys per tensor-core tile
 static constexpr int kKStages = MXDSA_K_STAGES;       // K ring depth (32 KB per stage and CTA); freed as soon as QK is done
 static constexpr int kVStages = MXDSA_V_STAGES;       // V ring depth (32 KB per stage and CTA); held until PV is done
+static constexpr int kSBufs = MXDSA_S_BUFS;      // S (quantised probabilities) ring: how far the softmax may run ahead of PV
 static constexpr int kScStages = 4;      // scale/validity ring depth; also the depth of the
                                          // per-tile "QK done" / "PV done" barrier rings
-// registers per thread that a launch of 384 + 128 G threads gets (65536 / threads, rounded down to a multiple of 8)
-__host__ __device__ constexpr int launch_regs(int g) { return g == 2 ? 96 : 80; }
-static constexpr int kBaseThreads = 384;   // warps 0-11: K producers, V producers, control; then G x 4 softmax warps
+// registers per thread that a launch of 512 + 128 G threads gets (65536 / threads, rounded down to a multiple of 8)
+__host__ __device__ constexpr int launch_regs(int g) { return g == 2 ? 80 : 72; }
+static constexpr int kBaseThreads = 512;   // warps 0-11: K producers, V producers, control; then G x 4 softmax warps; then 4 epilogue warps
 static constexpr int kMaxGroups = 3;     // softmax groups of four warps (template parameter G = 2 or 3); tile g is handled by group g % G
 
 // tensor-memory columns
@@ -84,8 +88,8 @@ static constexpr uint32_t kColO = 0;      // 256 columns
 static constexpr uint32_t kColP = 256;    // 2 buffers x 64
 static constexpr uint32_t kColQs = 384;   // 2 x 4 (one set per QK issuer): Q scale bytes 0-3 / 4-7 of rows 0-31, 32-63
 static constexpr uint32_t kColKs = 392;   // 2 x 4: K scale bytes 0-3 / 4-7 of keys 0-31, 32-63 of the half
-static constexpr uint32_t kColSs = 400;   // 2 buffers x 4 (2 used)
-static constexpr uint32_t kColVs = 408;   // 8: w words 0-7
+static constexpr uint32_t kColSs = 400;   // kSBufs x 4 (2 used)
+static constexpr uint32_t kColVs = 416;   // 8: w words 0-7
 static constexpr uint32_t kTmemCols = 512;
 
 struct DeviceFault {
@@ -156,11 +160,11 @@ struct __align__(1024) SmemPlan {
     uint8_t q[4 * 64 * 128];                       // [chunk][head][128 B], 128-byte swizzle
     uint8_t k[kKStages][4 * 64 * 128];             // [chunk][key of this CTA][128 B]
     uint8_t v[kVStages][2 * 128 * 128];            // [chunk of this CTA][key][128 B]
-    uint8_t s[2][64 * 128];                        // [row][128 keys], 128-byte swizzle
+    uint8_t s[kSBufs][64 * 128];                        // [row][128 keys], 128-byte swizzle
     __align__(16) uint16_t kvalid[kKStages][8];     // validity bits of the tile's keys, 16 per entry (K ring)
     __align__(128) uint32_t q_sf[64 * 4];          // scale rows for tcgen05.cp (64 rows x 16 B)
     __align__(128) uint32_t k_sf[kKStages][64 * 4];   // per K stage: K scale rows for tcgen05.cp, gathered by the producers with the rows
-    __align__(128) uint32_t s_sf[2][64 * 4];
+    __align__(128) uint32_t s_sf[kSBufs][64 * 4];
     __align__(16) float tok_scale[kScStages][kTileKeys];
     __align__(16) uint32_t valid[kScStages][4];
     float xmax[kMaxGroups][2][128];                   // [group][parity of the group's tile count][lane]: row max of the lane's 64 keys
@@ -170,17 +174,19 @@ struct __align__(1024) SmemPlan {
     uint64_t bar_q_full;                           // CTA0: Q data + scale rows of both CTAs ready
     uint64_t bar_q_empty;                          // both: every QK of the pair finished (2 arrivals)
     uint64_t bar_k_landed[kKStages];               // local: this CTA's K rows landed (128 arrivals)
-    uint64_t bar_v_landed[kVStages];               // local: this CTA's cp.async half of the V rows landed (128 arrivals)
-    uint64_t bar_v_full[kVStages];                 // CTA0: gather4 halves of both CTAs landed (8 arrivals + bytes), and CTA 1's cp.async half (1)
+    uint64_t bar_v_full[kVStages];                 // CTA0: V rows of both CTAs landed (8 arrivals + 64 KB of gather4 bytes)
     uint64_t bar_qk_done[kScStages];               // both: QK of tile g finished (ring by g % 4)
     uint64_t bar_pv_done[kScStages];               // both: PV of tile g finished
-    uint64_t bar_pv_half[2];                       // both: first key half accumulated (64-key tiles)
+    uint64_t bar_pv_half[kSBufs];                       // both: first key half accumulated (64-key tiles)
     uint64_t bar_sc_full[kScStages];               // CTA0: K scale rows of both CTAs written
     uint64_t bar_tok_full[kScStages];              // local: token scales + validity written
     uint64_t bar_tok_empty[kScStages];             // local: softmax has read the stage
     uint64_t bar_p_empty[2];                       // CTA0: P buffer copied to registers
-    uint64_t bar_s_full[2][2];                     // CTA0: [buffer][key half]
-    uint64_t bar_o_empty;                          // CTA0: epilogue has drained O
+    uint64_t bar_s_full[kSBufs][2];                     // CTA0: [buffer][key half]
+    float oscale[2][64];                           // [pair parity][row]: 1 / (l + sink term), what the epilogue multiplies O by
+    uint64_t bar_os_full[2];                       // local: oscale of the pair written (2 arrivals)
+    uint64_t bar_os_empty[2];                      // local: the epilogue warps have read it (4 arrivals)
+    uint64_t bar_o_empty;                          // CTA0: epilogue has drained O (4 warps of each CTA)
     uint64_t bar_m_ready[kMaxGroups];                 // local: group g published the running max of its tile
     uint32_t tmem_base;
     int abort_word;
@@ -574,12 +580,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             mbar_init(smem_u32(&sm.bar_k_landed[i]), 128 + 4);   // 128 copy completions + one plain arrival per producer warp
         }
         for (int i = 0; i < kVStages; ++i) {
-#ifndef MXDSA_V_SPLIT
             mbar_init(smem_u32(&sm.bar_v_full[i]), 8);
-#else
-            mbar_init(smem_u32(&sm.bar_v_full[i]), 9);
-#endif
-            mbar_init(smem_u32(&sm.bar_v_landed[i]), 128);
         }
         for (int i = 0; i < kScStages; ++i) {
             mbar_init(smem_u32(&sm.bar_qk_done[i]), 1);
@@ -588,13 +589,17 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             mbar_init(smem_u32(&sm.bar_tok_full[i]), 1);
             mbar_init(smem_u32(&sm.bar_tok_empty[i]), 4);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&sm.bar_p_empty[i]), 8);
+        for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&sm.bar_p_empty[i]), 8);
+        for (int i = 0; i < kSBufs; ++i) {
             mbar_init(smem_u32(&sm.bar_s_full[i][0]), 8);
             mbar_init(smem_u32(&sm.bar_s_full[i][1]), 8);
             mbar_init(smem_u32(&sm.bar_pv_half[i]), 1);
         }
-        mbar_init(smem_u32(&sm.bar_o_empty), 16);
+        mbar_init(smem_u32(&sm.bar_o_empty), 8);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&sm.bar_os_full[i]), 2);
+            mbar_init(smem_u32(&sm.bar_os_empty[i]), 4);
+        }
         for (int i = 0; i < kMaxGroups; ++i) mbar_init(smem_u32(&sm.bar_m_ready[i]), 4);
         sm.abort_word = 0;
         sm.fault = p.fault;
@@ -651,10 +656,15 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #ifdef MXDSA_X_REBAL_ALL
     constexpr bool kRebalanceRegs = true;
 #else
-    constexpr bool kRebalanceRegs = G == 3 || !DECODE;
+    constexpr bool kRebalanceRegs = true;
 #endif
-    constexpr int kRegsCopy = 64, kRegsGather = G == 2 ? 64 : 40, kRegsCtl = 64, kRegsSoftmax = G == 2 ? 144 : 104;
-    static_assert(4 * 32 * (kRegsCopy + kRegsGather + kRegsCtl) + 4 * G * 32 * kRegsSoftmax <= kThreads * kLaunchRegs,
+#ifdef MXDSA_RK
+    constexpr int kRegsCopy = MXDSA_RK, kRegsGather = MXDSA_RG, kRegsCtl = MXDSA_RC, kRegsEpi = MXDSA_RE;
+#else
+    constexpr int kRegsCopy = G == 2 ? 64 : 48, kRegsGather = G == 2 ? 40 : 32, kRegsCtl = 64, kRegsEpi = G == 2 ? 56 : 48;
+#endif
+    constexpr int kRegsSoftmax = G == 2 ? 128 : 104;
+    static_assert(4 * 32 * (kRegsCopy + kRegsGather + kRegsCtl + kRegsEpi) + 4 * G * 32 * kRegsSoftmax <= kThreads * kLaunchRegs,
                   "register budget must fit in the launch allocation");
     if (warp < 8) {
         if (warp < 4) {
@@ -745,7 +755,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 const void* map = key_rows4<DECODE>(p, maps, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64, ix, r);
                 cv.advance();
                 if (cv.live) ix = key_index4<DECODE>(p, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64);
-#ifndef MXDSA_V_SPLIT
                 if (lane == 0) mbar_expect_tx_cluster(v_full0 + s * 8, 2 * 32 * 128);
                 __syncwarp();
                 if (lane < 8) {
@@ -754,32 +763,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     tma_gather4_pair(dst + 16384, map, 256 * (int)cta + 128, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
                 }
                 __syncwarp();
-#else
-                // The copy engine alone needs longer for a tile's 32 KB than the tile should take, and so would
-                // the cp.async path if it carried V on top of K: chunk 0 goes by gather4, chunk 1 by cp.async.
-                if (lane == 0) mbar_expect_tx_cluster(v_full0 + s * 8, 32 * 128);
-                __syncwarp();
-                if (lane < 8)
-                    tma_gather4_pair(v_dst0 + s * 32768, map, 256 * (int)cta, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
-                __syncwarp();
-                {
-                    // a row coordinate r of the 2-D view is byte offset 512 r of the store
-                    const uint8_t* base = (DECODE && map == static_cast<const void*>(&maps.ekv)) ? p.extra_kv : p.kv;
-                    const uint32_t dst1 = smem_u32(sm.v[0]) + s * 32768 + 16384;
-#pragma unroll 2
-                    for (int i = 0; i < 8; ++i) {   // instruction i: keys 4i .. 4i+3 of this warp's 32 (owned by lane i), 128 bytes each
-                        const int c0 = __shfl_sync(0xffffffffu, r[0], i), c1 = __shfl_sync(0xffffffffu, r[1], i);
-                        const int c2 = __shfl_sync(0xffffffffu, r[2], i), c3 = __shfl_sync(0xffffffffu, r[3], i);
-                        const int sub = lane >> 3;
-                        const int rr = sub == 0 ? c0 : sub == 1 ? c1 : sub == 2 ? c2 : c3;
-                        const int k = 32 * pw + 4 * i + sub;
-                        cp_async16(dst1 + k * 128 + (((lane & 7) ^ (k & 7)) << 4),
-                                   rr >= 0 ? base + (long long)rr * 512 + 256 * (int)cta + 128 + (lane & 7) * 16 : p.kv,
-                                   rr >= 0 ? 16u : 0u);
-                    }
-                    cp_async_arrive(smem_u32(&sm.bar_v_landed[s]));
-                }
-#endif
                 if (pw == 0 && lane == 0) { MXDSA_EV(vt, 3) }
                 ++vt;
             }
@@ -878,13 +861,9 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 #pragma unroll 1
                 for (int t = 0; t < ntiles; ++t, ++gt) {
                     const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
-                    const uint32_t b = gt & 1, bph = (gt >> 1) & 1;
+                    const uint32_t b = gt % kSBufs, bph = (gt / kSBufs) & 1;   // S buffer and the phase of its barriers
                     const uint32_t sc = gt % kScStages;
                     MXDSA_WAIT_TIGHT(sm.bar_v_full[s], ph, 34);
-#ifdef MXDSA_V_SPLIT
-                    MXDSA_WAIT_TIGHT(sm.bar_v_landed[s], ph, 31);
-                    fence_proxy_async_smem();   // rows written by cp.async are read by the tensor core
-#endif
                     const uint64_t a_base = smem_desc(desc_k128, smem_u32(sm.s[b]));
                     const uint64_t b_base = smem_desc(desc_v, smem_u32(sm.v[s]));
                     const uint32_t sfa = tmem + kColSs + 4 * b;
@@ -921,26 +900,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 }
                 ++gw;
             }
-#ifdef MXDSA_V_SPLIT
-        } else if (lane == 0) {
-            // ===================== V relay (CTA 1): tells CTA 0 that this CTA's cp.async half has landed =====
-            WorkIter<DECODE> it(p);
-            WorkItem w;
-            uint32_t gt = 0;
-            const uint32_t v_full0 = map_to_cta(smem_u32(&sm.bar_v_full[0]), 0);
-#pragma unroll 1
-            while (it.template next<NT>(w)) {
-                const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
-                if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
-#pragma unroll 1
-                for (int t = 0; t < ntiles; ++t, ++gt) {
-                    const uint32_t s = gt % kVStages, ph = (gt / kVStages) & 1;
-                    MXDSA_WAIT_THREAD(sm.bar_v_landed[s], ph, 13);
-                    fence_proxy_async_smem();
-                    mbar_arrive_cluster(v_full0 + s * 8);
-                }
-            }
-#endif
         }
     } else if (warp == 11) {
         // ===================== operand stager =====================
@@ -1026,7 +985,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             ++gw;
         }
     }
-    } else {
+    } else if (warp < 12 + 4 * G) {
         if constexpr (kRebalanceRegs) setmaxnreg_inc<kRegsSoftmax>();
         // ===================== softmax + epilogue (warps 12 ..) =====================
         // Two groups of four warps take alternate tiles (group = tile parity = P buffer), so one
@@ -1043,7 +1002,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         const uint32_t lane_addr = tmem + (uint32_t(q4 * 32) << 16);
         const uint32_t p_empty0 = map_to_cta(smem_u32(&sm.bar_p_empty[0]), 0);
         const uint32_t s_full0 = map_to_cta(smem_u32(&sm.bar_s_full[0][0]), 0);
-        const uint32_t o_empty0 = map_to_cta(smem_u32(&sm.bar_o_empty), 0);
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         WorkIter<DECODE> it(p);
         WorkItem w;
@@ -1058,7 +1016,8 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             for (int t = 0; t < ntiles; ++t, ++gt) {
                 if ((int)(gt % kGroups) != grp) continue;
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
-                const uint32_t b = gt & 1, bph = (gt >> 1) & 1;   // P and S buffer of the tile and the phase of their barriers
+                const uint32_t pb = gt & 1;                              // P buffer
+                const uint32_t b = gt % kSBufs, bph = (gt / kSBufs) & 1;   // S buffer and the phase of its barriers
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 22) }
                 MXDSA_WAIT_POLL(sm.bar_tok_full[sc], sph, 50);
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 23) }
@@ -1067,12 +1026,12 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 8) }
                 tc_fence_after();
                 float x[64];
-                tmem_ld32(lane_addr + kColP + b * 64, reinterpret_cast<uint32_t*>(x));
-                tmem_ld32(lane_addr + kColP + b * 64 + 32, reinterpret_cast<uint32_t*>(x + 32));
+                tmem_ld32(lane_addr + kColP + pb * 64, reinterpret_cast<uint32_t*>(x));
+                tmem_ld32(lane_addr + kColP + pb * 64 + 32, reinterpret_cast<uint32_t*>(x + 32));
                 tmem_wait_ld();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(p_empty0 + b * 8);
+                if (lane == 0) mbar_arrive_cluster(p_empty0 + pb * 8);
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 9) }
                 if ((v0 & v1) != 0xffffffffu) {
 #pragma unroll
@@ -1126,9 +1085,9 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 sm.m_pub[grp][row] = m_own;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&sm.bar_m_ready[grp]));
-                // S buffer b is free once the PV of tile gt-2 has finished (long ago, as a rule)
-                if (gt >= 2) {
-                    const uint32_t g = gt - 2;
+                // S buffer b is free once the PV of tile gt - kSBufs has finished (long ago, as a rule)
+                if (gt >= (uint32_t)kSBufs) {
+                    const uint32_t g = gt - kSBufs;
                     MXDSA_WAIT_POLL(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 52);
                 }
                 if (warp == 12 && lane == 0) { MXDSA_EV(gt, 19) }
@@ -1241,45 +1200,77 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 real_all = fmaxf(real_all, fmaxf(xr[256 + row], xr[320 + row]));
             }
             named_bar_sync(1 + kGroups, kGroups * 128);   // everybody has read the exchange area before the next pair writes it
-            // Two groups drain O, 128 columns per thread; the group whose turn the next tile is goes straight on
-            // to the next pair, so that its softmax overlaps the drain.
-            const int drain = kGroups == 2 ? grp : (grp - (int)((last + 1) % kGroups) + kGroups) % kGroups - 1;   // -1: not draining
-            if (drain < 0) {
-                ++gw;
-                continue;
+            // The first two warps of group 0 (one thread per row) turn the row sums into what the epilogue warps
+            // need, write lse / max_logits, and every softmax warp goes straight on to the next pair: O is drained
+            // by warps of its own while the next pair's tiles are worked on.
+            if (grp == 0 && half == 0) {
+                float m = m_fin;
+                if (real_all == -CUDART_INF_F) {
+                    l_tot = 0.f;
+                    m = -CUDART_INF_F;
+                }
+                const int tok_idx = 2 * w.pair + (int)cta;
+                const float sink = p.attn_sink ? __ldg(p.attn_sink + row) : -CUDART_INF_F;
+                float oscale;
+                if (!DECODE || !w.split) oscale = __fdividef(1.0f, l_tot + ex2_approx(fmaf(sink, CUDART_L2E_F, -m)));
+                else oscale = __fdividef(1.0f, l_tot);
+                if (l_tot == 0.f) oscale = 0.f;
+                if (tok_idx < p.s_q) {
+                    if (!DECODE || !w.split) {
+                        float lse = fmaf(m, CUDART_LN2_F, CUDART_LN2_F * lg2_approx(l_tot));
+                        if (l_tot == 0.f || lse == -CUDART_INF_F) lse = CUDART_INF_F;
+                        const long long o = ((long long)w.req * p.s_q + tok_idx) * kHeads + row;
+                        p.lse[o] = lse;
+                        if (!DECODE) p.max_logits[o] = real_all * CUDART_LN2_F;
+                    } else {
+                        p.lse_accum[((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row] = lg2_approx(l_tot) + m;
+                    }
+                }
+                // oscale is handed over through a two-deep buffer: slot gw & 1 was last used by pair gw - 2
+                if (gw >= 2) MXDSA_WAIT_POLL(sm.bar_os_empty[gw & 1], ((gw >> 1) & 1) ^ 1, 56);
+                sm.oscale[gw & 1][row] = oscale;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sm.bar_os_full[gw & 1]));
             }
-            float m = m_fin;
-            if (real_all == -CUDART_INF_F) {
-                l_tot = 0.f;
-                m = -CUDART_INF_F;
-            }
-            MXDSA_WAIT_POLL(sm.bar_pv_done[last % kScStages], (last / kScStages) & 1, 55);
+            ++gw;
+        }
+    } else {
+        if constexpr (kRebalanceRegs) setmaxnreg_dec<kRegsEpi>();
+        // ===================== epilogue (last four warps): O -> out =====================
+        // A thread drains its tensor-memory lane: row L%64, the 256 dims of half L/64, 32 columns at a time,
+        // multiplied by the row's oscale.  Unsplit work goes to `out` as bf16, split decode work to the fp32
+        // partials.  The next pair's first PV waits for "O drained"; everything else of the next pair (gathers,
+        // QK, softmax) runs meanwhile.
+        const int q4 = warp & 3;
+        const int L = q4 * 32 + lane;
+        const int row = L % 64;
+        const int half = L / 64;
+        const uint32_t lane_addr = tmem + (uint32_t(q4 * 32) << 16);
+        const uint32_t o_empty0 = map_to_cta(smem_u32(&sm.bar_o_empty), 0);
+        WorkIter<DECODE> it(p);
+        WorkItem w;
+        uint32_t gt = 0, gw = 0;
+#pragma unroll 1
+        while (it.template next<NT>(w)) {
+            const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
+            if (ntiles <= 0) continue;  // never produced by the scheduler; keeps the roles in step
+            gt += ntiles;
+            const uint32_t last = gt - 1;
+            MXDSA_WAIT(sm.bar_os_full[gw & 1], (gw >> 1) & 1, 60);
+            const float oscale = sm.oscale[gw & 1][row];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm.bar_os_empty[gw & 1]));
+            MXDSA_WAIT(sm.bar_pv_done[last % kScStages], (last / kScStages) & 1, 55);
             tc_fence_after();
+            if (lane == 0 && q4 == 0) { MXDSA_EVW2(last, 18) }
             const int tok_idx = 2 * w.pair + (int)cta;
             const bool store = tok_idx < p.s_q;
-            const float sink = p.attn_sink ? __ldg(p.attn_sink + row) : -CUDART_INF_F;
-            float oscale;
-            if (!DECODE || !w.split) oscale = __fdividef(1.0f, l_tot + ex2_approx(fmaf(sink, CUDART_L2E_F, -m)));
-            else oscale = __fdividef(1.0f, l_tot);
-            if (l_tot == 0.f) oscale = 0.f;
-            if (drain == 0 && half == 0 && store) {
-                if (!DECODE || !w.split) {
-                    float lse = fmaf(m, CUDART_LN2_F, CUDART_LN2_F * lg2_approx(l_tot));
-                    if (l_tot == 0.f || lse == -CUDART_INF_F) lse = CUDART_INF_F;
-                    const long long o = ((long long)w.req * p.s_q + tok_idx) * kHeads + row;
-                    p.lse[o] = lse;
-                    if (!DECODE) p.max_logits[o] = real_all * CUDART_LN2_F;
-                } else {
-                    p.lse_accum[((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row] = lg2_approx(l_tot) + m;
-                }
-            }
-            const int dim0 = half * 256 + drain * 128;   // this thread's 128 output dims
             if (!DECODE || !w.split) {
-                __nv_bfloat16* dst = p.out + (((long long)w.req * p.s_q + tok_idx) * kHeads + row) * kDim + dim0;
+                __nv_bfloat16* dst = p.out + (((long long)w.req * p.s_q + tok_idx) * kHeads + row) * kDim + half * 256;
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
+                for (int c = 0; c < 256; c += 32) {
                     float o[32];
-                    tmem_ld32(lane_addr + kColO + drain * 128 + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_ld32(lane_addr + kColO + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
                         // 32 columns -> 64 bytes of bf16: two 32-byte stores per lane (whole sectors; sixteen-byte
@@ -1299,11 +1290,11 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     }
                 }
             } else {
-                float* dst = p.o_accum + (((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row) * kDim + dim0;
+                float* dst = p.o_accum + (((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row) * kDim + half * 256;
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
+                for (int c = 0; c < 256; c += 32) {
                     float o[32];
-                    tmem_ld32(lane_addr + kColO + drain * 128 + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_ld32(lane_addr + kColO + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
@@ -1318,6 +1309,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     }
                 }
             }
+            if (lane == 0 && q4 == 0) { MXDSA_EVW2(last, 21) }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(o_empty0);
@@ -1330,7 +1322,7 @@ done:
     // After a fault, softmax threads leave at different points; one extra arrival per leaving thread
     // completes the exchange barrier for those still parked on it (they fail their next wait and
     // follow).  In a normal exit the arrivals are harmless: nobody waits on that barrier any more.
-    if (warp >= 12) {
+    if (warp >= 12 && warp < 12 + 4 * G) {
         named_bar_arrive(1 + ((warp - 12) >> 2), 128);
         named_bar_arrive(1 + kGroups, kGroups * 128);
     }
