@@ -11,25 +11,30 @@
 //   accumulators live in tensor memory: per CTA 128 lanes x (256 O + 2 x 64 P) columns; lane L
 //   holds row L%64, and column half L/64 (P: keys 64*(L/64).., O: dims 256*(L/64)..).
 //
-// Roles (warp-specialised, 20 warps per CTA; 96 registers per thread at launch, re-balanced in prefill to
-// 64 for the copy and control warps and 144 for the softmax warps)
-//   warps 0-3   K producers (one instruction stream with the V producers): read key indices and copy the
-//               selected rows of this CTA's 64 keys
-//               into a 2-deep K ring with 16-byte cp.async; one warp instruction moves one
-//               512-byte row straight into the 128-byte-swizzled operand layout.  Measured on a
-//               B200 this path sustains ~40 B/clk/SM of random 512-byte rows from L2 with eight
-//               issuing warps (about 9 B/clk per warp), against ~21 B/clk/SM for TMA gather4.
-//   warps 4-7   V producers: same for the 256-byte halves of all 128 keys (3-deep V ring)
-//   warp 8      CTA 0: QK issuer for even tiles      CTA 1: relays "K rows landed" to CTA 0
-//               (issuers run as converged warps, one elected lane issues fully unrolled MMAs)
-//   warp 9      CTA 0: QK issuer for odd tiles       (each with its own P buffer and scale columns)
-//   warp 10     CTA 0: PV issuer                     CTA 1: relays "V rows landed" to CTA 0
-//   warp 11     operand stager: Q tile TMA + Q scale rows (per pair); K scale rows, key token
-//               scales and validity bits (per tile), index and slot loads two tiles deep
-//   warps 12-19 softmax: two groups of four warps take alternate tiles (each thread one row and one
-//               64-key half of its tile): P -> registers, running max with lazy rescale handed
-//               from group to group, exp2, token-scale, per-32-key UE8M0 requantisation to E4M3
-//               S, O rescale; both groups share the epilogue.
+// Roles (warp-specialised, 28 warps per CTA; the launch gives every thread 72 registers, re-balanced with
+// setmaxnreg to 48 / 32 / 64 / 104 / 48 for the five kinds of warp below)
+//   warps 0-3   K producers: read key indices one tile ahead and copy the selected rows of this CTA's 64 keys
+//               into the K ring with 16-byte cp.async; one warp instruction moves one 512-byte row straight
+//               into the 128-byte-swizzled operand layout.  The same warps gather the 8 scale bytes of all 128
+//               keys of the tile into the row layout that tcgen05.cp wants, and vote the validity bits.
+//   warps 4-7   V producers: TMA gather4 (four rows x 128 bytes per request) of the 256-byte halves of all 128
+//               keys into the V ring; eight lanes per warp issue.  The bytes of both CTAs complete on one
+//               barrier of CTA 0.  (cp.async carrying V as well makes the K rows -- which the next QK waits
+//               for -- land late; the copy engine alone is the slower of the two paths, which is why K is not
+//               on it.)
+//   warp 8      CTA 0: QK issuer for even tiles      (issuers run as converged warps, one elected lane
+//   warp 9      CTA 0: QK issuer for odd tiles        issues fully unrolled MMAs; each has its own P buffer
+//   warp 10     CTA 0: PV issuer                      and scale columns)
+//   warp 11     operand stager: Q tile by TMA + Q scale rows per pair (the next pair's tile is requested into
+//               L2 a pair ahead); per tile it waits for "K landed", fences and publishes "scale rows ready"
+//               to CTA 0 -- no global load sits between a landed K tile and its QK -- then derives the key
+//               token scales and validity words that the softmax reads.
+//   warps 12-23 softmax: three groups of four warps take tiles in turn (each thread one row and one 64-key
+//               half of its tile): P -> registers, running max with lazy rescale handed from group to group,
+//               exp2, token scale, per-32-key UE8M0 requantisation to E4M3 S (ring of three), O rescale.
+//               At the end of a pair the groups add up their row sums and hand 1/l to the epilogue warps.
+//   warps 24-27 epilogue: drain O (tensor memory -> bf16 `out`, or fp32 split partials) while the other
+//               warps are already working on the next pair; only that pair's first PV waits for the drain.
 //
 // Numerical contract (identical to the reference kernels, reference file:line in brackets)
 //   * keys are consumed in numerical tiles of NT = 128 (prefill, topk >= 512) or 64 keys
@@ -134,7 +139,6 @@ struct AttnParams {
     float* lse_accum;         // [splits][s_q][64]
     int page_shift, extra_page_shift;         // log2(page size) when it is a power of two, else -1
     long long pool_rows, extra_pool_rows;     // decode: keys in each pool (num_blocks * page_size); indices beyond are skipped
-    unsigned long long* prof; // profiling builds: [2 CTAs][64] stall cycles of cluster 0, else null
 };
 
 struct TensorMaps {
@@ -191,9 +195,6 @@ struct __align__(1024) SmemPlan {
     uint32_t tmem_base;
     int abort_word;
     DeviceFault* fault;                            // copy of the kernel parameter, for the out-of-line wait path
-#ifdef MXDSA_PROFILE
-    unsigned long long prof[64];
-#endif
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -287,9 +288,6 @@ __device__ __forceinline__ int key_index(const AttnParams& p, const WorkItem& w,
     if (blk >= w.blk_end) return -1;
     if constexpr (!DECODE) {
         const int pos = blk * 64 + j;
-#ifdef MXDSA_X_FAKEIDX
-        return pos < p.topk ? (int)(((unsigned)(pos + w.pair) * 40503u) & (unsigned)(p.s_kv - 1)) : -1;
-#endif
         return pos < p.topk ? __ldg(w.row + pos) : -1;
     } else {
         const bool extra = blk >= w.n_main_blocks;
@@ -462,53 +460,14 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
-#ifdef MXDSA_PROFILE
-#ifndef MXDSA_EV_CTA
-#define MXDSA_EV_CTA 0
-#endif
-#define MXDSA_EV_STORE(gtile, id) { if (blockIdx.x == MXDSA_EV_CTA && blockIdx.y == 0 && p.prof != nullptr) p.prof[128 + ((gtile)-16) * 24 + (id)] = (unsigned long long)(clock64() - prof_kernel_t0); }
-// per-wait stall accounting (cycles spent in each numbered wait, summed over the lanes' leader)
-#ifdef MXDSA_PROFILE_LIGHT   // event stamps only, and only those of MXDSA_EV_MASK: perturbs the timeline far less
-#define MXDSA_PROF_BEGIN
-#define MXDSA_PROF_END(code)
-#else
-#define MXDSA_PROF_BEGIN const long long prof_t0__ = clock64();
-#define MXDSA_PROF_END(code) \
-    if (lane == 0) atomicAdd(&sm.prof[(code)], (unsigned long long)(clock64() - prof_t0__));
-#endif
-#ifndef MXDSA_EV_MASK
-#define MXDSA_EV_MASK 0xffffffu
-#endif
-// event trace: cycle stamps of tiles 16..31 of this CTA (profiling builds only)
-#ifdef MXDSA_X_WARPEV
-#define MXDSA_EV(gtile, id)
-#define MXDSA_EVW2(gtile, id)
-#define MXDSA_EVW(gtile, id) \
-    if ((gtile) >= 16 && (gtile) < 32) MXDSA_EV_STORE(gtile, id)
-#else
-#define MXDSA_EVW(gtile, id)
-#ifdef MXDSA_X_QKEV
-#define MXDSA_EVW2(gtile, id) if ((gtile) >= 16 && (gtile) < 32) MXDSA_EV_STORE(gtile, id)
-#else
-#define MXDSA_EVW2(gtile, id)
-#endif
-#define MXDSA_EV(gtile, id) \
-    if ((((MXDSA_EV_MASK) >> (id)) & 1u) && (gtile) >= 16 && (gtile) < 32) MXDSA_EV_STORE(gtile, id)
-#endif
-#else
-#define MXDSA_EVW(gtile, id)
-#define MXDSA_EVW2(gtile, id)
-#define MXDSA_PROF_BEGIN
-#define MXDSA_PROF_END(code)
-#define MXDSA_EV(gtile, id)
-#endif
 
-// Bounded waits, called by whole warps unless stated otherwise.  Every lane watches the barrier
-// itself: electing one lane and broadcasting the outcome was measured 50% slower end to end.
-//   MXDSA_WAIT       suspending wait (producers, stager)
+// Bounded waits, always called by whole, converged warps.  Every lane watches the barrier itself and takes
+// the decision itself: all lanes of a warp execute the same barrier test in the same instruction and get the
+// same answer, so the warp stays together.  (Two alternatives were measured: one elected lane that polls and
+// broadcasts the outcome costs 35-50% end to end; a warp vote on every decision costs 5-9% at topk 4096.)
+//   MXDSA_WAIT       suspending wait (producers, stager, epilogue)
 //   MXDSA_WAIT_POLL  polling with a short back-off (softmax)
-//   MXDSA_WAIT_TIGHT polling without back-off (MMA issuers)
-//   MXDSA_WAIT_THREAD  suspending wait for a role that runs as a single thread (relays)
+//   MXDSA_WAIT_TIGHT polling without back-off (MMA issuers, stager on "K landed")
 #ifndef MXDSA_POLL_BACKOFF_NS
 #define MXDSA_POLL_BACKOFF_NS 40
 #endif
@@ -516,10 +475,9 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 // only call -- raise_fault -- sits on the path that never comes back, so no register has to survive
 // it: a call on the waiting path costs about 1 KB of save/restore code per site, and the kernel's
 // instruction footprint is what limits it (the SM's instruction cache holds about 32 KB).
-// Bounds: polling 2^24 tries (>= 0.2 s), suspending 6000 slices of 100 us.
+// Bounds: polling 2^24 tries (>= 0.2 s), suspending kWaitSlices slices of kWaitSliceNs.
 #define MXDSA_WAIT_ADDR_(mode, addr, parity, code)                                                  \
     do {                                                                                            \
-        MXDSA_PROF_BEGIN                                                                            \
         if (__builtin_expect(!mbar_try_wait((addr), (parity)), 0)) {                                \
             uint32_t spins__ = 0;                                                                   \
             while (true) {                                                                          \
@@ -540,15 +498,10 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
                 }                                                                                   \
             }                                                                                       \
         }                                                                                           \
-        MXDSA_PROF_END(code)                                                                        \
     } while (0)
 #define MXDSA_WAIT_POLL(bar, parity, code) MXDSA_WAIT_ADDR_(MXDSA_POLL_BACKOFF_NS, smem_u32(&(bar)), parity, code)
-#ifndef MXDSA_TIGHT_BACKOFF_NS
-#define MXDSA_TIGHT_BACKOFF_NS 0
-#endif
-#define MXDSA_WAIT_TIGHT(bar, parity, code) MXDSA_WAIT_ADDR_(MXDSA_TIGHT_BACKOFF_NS, smem_u32(&(bar)), parity, code)
+#define MXDSA_WAIT_TIGHT(bar, parity, code) MXDSA_WAIT_ADDR_(0, smem_u32(&(bar)), parity, code)
 #define MXDSA_WAIT(bar, parity, code) MXDSA_WAIT_ADDR_(-1, smem_u32(&(bar)), parity, code)
-#define MXDSA_WAIT_THREAD(bar, parity, code) MXDSA_WAIT_ADDR_(-1, smem_u32(&(bar)), parity, code)
 
 // A wait was abandoned: mark both CTAs of the pair and the device fault record.
 __device__ __noinline__ void raise_fault(SmemPlan& sm, int code) {
@@ -603,14 +556,8 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         for (int i = 0; i < kMaxGroups; ++i) mbar_init(smem_u32(&sm.bar_m_ready[i]), 4);
         sm.abort_word = 0;
         sm.fault = p.fault;
-#ifdef MXDSA_PROFILE
-        for (int i = 0; i < 64; ++i) sm.prof[i] = 0;
-#endif
         fence_mbar_init();
     }
-#ifdef MXDSA_PROFILE
-    const long long prof_kernel_t0 = clock64();
-#endif
     if (warp == 11 && lane == 0) prefetch_tensormap(&maps.q);
     __syncthreads();
     cluster_sync();
@@ -653,16 +600,8 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     constexpr int kGroups = G;
     constexpr int kThreads = kBaseThreads + 128 * G;
     constexpr int kLaunchRegs = launch_regs(G);
-#ifdef MXDSA_X_REBAL_ALL
     constexpr bool kRebalanceRegs = true;
-#else
-    constexpr bool kRebalanceRegs = true;
-#endif
-#ifdef MXDSA_RK
-    constexpr int kRegsCopy = MXDSA_RK, kRegsGather = MXDSA_RG, kRegsCtl = MXDSA_RC, kRegsEpi = MXDSA_RE;
-#else
     constexpr int kRegsCopy = G == 2 ? 64 : 48, kRegsGather = G == 2 ? 40 : 32, kRegsCtl = 64, kRegsEpi = G == 2 ? 56 : 48;
-#endif
     constexpr int kRegsSoftmax = G == 2 ? 128 : 104;
     static_assert(4 * 32 * (kRegsCopy + kRegsGather + kRegsCtl + kRegsEpi) + 4 * G * 32 * kRegsSoftmax <= kThreads * kLaunchRegs,
                   "register budget must fit in the launch allocation");
@@ -689,7 +628,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const uint32_t g = kt - kKStages;
                     MXDSA_WAIT(sm.bar_qk_done[g % kScStages], (g / kScStages) & 1, 10);
                 }
-                if (pw == 0 && lane == 0) { MXDSA_EV(kt, 0) }
                 const uint8_t* cur;
                 const uint8_t* slot;
                 uint32_t vbits;
@@ -722,7 +660,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     sm.kvalid[s][4 * (1 - cta) + pw] = (uint16_t)(vbits >> 16);
                     mbar_arrive(smem_u32(&sm.bar_k_landed[s]));
                 }
-                if (pw == 0 && lane == 0) { MXDSA_EV(kt, 1) }
                 ++kt;
             }
         } else {
@@ -750,7 +687,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const uint32_t g = vt - kVStages;
                     MXDSA_WAIT(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 11);
                 }
-                if (pw == 0 && lane == 0) { MXDSA_EV(vt, 2) }
                 int r[4];
                 const void* map = key_rows4<DECODE>(p, maps, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64, ix, r);
                 cv.advance();
@@ -763,7 +699,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     tma_gather4_pair(dst + 16384, map, 256 * (int)cta + 128, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
                 }
                 __syncwarp();
-                if (pw == 0 && lane == 0) { MXDSA_EV(vt, 3) }
                 ++vt;
             }
         }
@@ -800,13 +735,10 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                     const uint32_t bph = (gt >> 1) & 1;
                     MXDSA_WAIT_TIGHT(sm.bar_sc_full[sc], sph, 21);
-                    MXDSA_EVW2(gt, 16)
                     MXDSA_WAIT_TIGHT(sm.bar_p_empty[e], bph ^ 1, 22);
-                    MXDSA_EVW2(gt, 17)
                     // "scale rows ready" comes from the stagers of both CTAs, each of which has seen its CTA's K rows
                     // land and has fenced them towards the tensor core: nothing else to wait for
                     fence_proxy_async_smem();
-                    MXDSA_EV(gt, 6)
                     tc_fence_after();
                     __syncwarp();
                     if (elect_one()) {
@@ -828,7 +760,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     }
                     __syncwarp();
                     mine = true;
-                    MXDSA_EV(gt, 7)
                 }
                 // Q may be overwritten once both issuers' QKs of this pair have finished
                 if (elect_one()) {
@@ -872,8 +803,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     for (int h = 0; h < 2; ++h) {
                         if (NT == 128 && h == 0) continue;   // 128-key tiles: one wait, after both halves are in
                         MXDSA_WAIT_TIGHT(sm.bar_s_full[b][h], bph, 32 + h);
-                        MXDSA_EV(gt, 13 + h)
-                        MXDSA_EVW(gt, 16)
                         tc_fence_after();
                         __syncwarp();
                         if (elect_one()) {
@@ -896,7 +825,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                         }
                         __syncwarp();
                     }
-                    MXDSA_EV(gt, 15)
                 }
                 ++gw;
             }
@@ -954,15 +882,12 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             for (int t = 0; t < ntiles; ++t) {
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                 const uint32_t ks = gt % kKStages;
-                MXDSA_EV(gt, 13)
                 MXDSA_WAIT_TIGHT(sm.bar_k_landed[ks], (gt / kKStages) & 1, 44);
-                MXDSA_EV(gt, 5)
                 // The K rows, the scale rows and the validity bits of this CTA have landed.  Publish at once (the
                 // fence makes what cp.async wrote visible to the tensor core), then derive what the softmax reads.
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(sc_full0 + sc * 8);
-                MXDSA_EV(gt, 4)
                 // token scale = 2^(scale byte 0 - 127); keys L, L+32 sit in words 0, 1 of row L, keys L+64, L+96 in row 32+L
                 const uint2 lo = *reinterpret_cast<const uint2*>(&sm.k_sf[ks][lane * 4]);
                 const uint2 hi = *reinterpret_cast<const uint2*>(&sm.k_sf[ks][(32 + lane) * 4]);
@@ -1018,12 +943,9 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 const uint32_t sc = gt % kScStages, sph = (gt / kScStages) & 1;
                 const uint32_t pb = gt & 1;                              // P buffer
                 const uint32_t b = gt % kSBufs, bph = (gt / kSBufs) & 1;   // S buffer and the phase of its barriers
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 22) }
                 MXDSA_WAIT_POLL(sm.bar_tok_full[sc], sph, 50);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 23) }
                 const uint32_t v0 = sm.valid[sc][2 * half], v1 = sm.valid[sc][2 * half + 1];
                 MXDSA_WAIT_POLL(sm.bar_qk_done[sc], sph, 51);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 8) }
                 tc_fence_after();
                 float x[64];
                 tmem_ld32(lane_addr + kColP + pb * 64, reinterpret_cast<uint32_t*>(x));
@@ -1032,7 +954,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(p_empty0 + pb * 8);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 9) }
                 if ((v0 & v1) != 0xffffffffu) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) x[i] = (((i < 32 ? v0 : v1) >> (i & 31)) & 1u) ? x[i] : -CUDART_INF_F;
@@ -1048,15 +969,12 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 const float own_max = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * p.scale_log2;
                 float* xm = sm.xmax[grp][(gt / kGroups) & 1];
                 xm[L] = own_max;
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 16) }
                 named_bar_sync(1 + grp, 128);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 17) }
                 const float peer_max = xm[L ^ 64];
                 // the running maximum handed over by the other group (value ignored on a pair's first
                 // tile, but every phase of that barrier is observed)
                 if (gt > 0) MXDSA_WAIT_POLL(sm.bar_m_ready[prev_grp], ((gt - 1) / kGroups) & 1, 58);
                 const float m_prev = t == 0 ? -1e30f : sm.m_pub[prev_grp][row];
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 10) }
                 const float sprev = (m_own == m_prev) ? 1.f : ex2_approx(m_own - m_prev);
                 // numerical tiles: NT = 128 -> one per tensor-core tile; NT = 64 -> key half 0 then 1
                 float m_used, scale0 = 1.f, scale1 = 1.f;
@@ -1090,7 +1008,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const uint32_t g = gt - kSBufs;
                     MXDSA_WAIT_POLL(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 52);
                 }
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 19) }
                 // probabilities, key-scaled, re-quantised per 32 keys and stored
                 const float2 negm2 = make_float2(-m_used, -m_used);
                 const float4* tok4 = reinterpret_cast<const float4*>(&sm.tok_scale[sc][half * 64]);
@@ -1123,7 +1040,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     e = max(e, 61u);
                     const float mulf = __uint_as_float((254u - e) << 23);
                     const float2 mul2 = make_float2(mulf, mulf);
-                    if (g == 0 && warp == 12 && lane == 0) { MXDSA_EV(gt, 18) }
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
                         const float2 a = f2_mul(make_float2(xg[i], xg[i + 1]), mul2);
@@ -1146,25 +1062,17 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     if (half == 0) l = fmaf(l * sprev, scale0, sum) * scale1;
                     else l = fmaf(l * sprev * scale0, scale1, sum);
                 }
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 11) }
                 // O rescale before the first key half is accumulated (this thread: its whole lane)
-#ifndef MXDSA_X_NORESCALE
                 if (grow0 && t > 0)
-#else
-                if (false)
-#endif
                 {
                     MXDSA_WAIT_POLL(sm.bar_pv_done[(gt - 1) % kScStages], ((gt - 1) / kScStages) & 1, 53);
                     tc_fence_after();
                     rescale_o(lane_addr, scale0);
                     tc_fence_before();
                 }
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 20) }
                 fence_proxy_async_smem();
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 21) }
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(s_full0 + (b * 2 + 0) * 8);
-                if (warp == 12 && lane == 0) { MXDSA_EV(gt, 12) }
                 if constexpr (NT == 64) {
                     if (grow1) {
                         MXDSA_WAIT_POLL(sm.bar_pv_half[b], bph, 54);
@@ -1262,7 +1170,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             if (lane == 0) mbar_arrive(smem_u32(&sm.bar_os_empty[gw & 1]));
             MXDSA_WAIT(sm.bar_pv_done[last % kScStages], (last / kScStages) & 1, 55);
             tc_fence_after();
-            if (lane == 0 && q4 == 0) { MXDSA_EVW2(last, 18) }
             const int tok_idx = 2 * w.pair + (int)cta;
             const bool store = tok_idx < p.s_q;
             if (!DECODE || !w.split) {
@@ -1309,7 +1216,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     }
                 }
             }
-            if (lane == 0 && q4 == 0) { MXDSA_EVW2(last, 21) }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(o_empty0);
@@ -1328,12 +1234,6 @@ done:
     }
     tc_fence_before();
     __syncthreads();
-#ifdef MXDSA_PROFILE
-    if (p.prof != nullptr && blockIdx.x < 2 && blockIdx.y == 0 && threadIdx.x < 64) {
-        if (threadIdx.x == 0) sm.prof[0] = (unsigned long long)(clock64() - prof_kernel_t0);
-        p.prof[blockIdx.x * 64 + threadIdx.x] = sm.prof[threadIdx.x];
-    }
-#endif
     cluster_sync();
     if (warp == 10) tmem_dealloc<2>(tmem, kTmemCols);
 }

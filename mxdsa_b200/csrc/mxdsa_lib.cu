@@ -28,10 +28,7 @@ thread_local int tl_last_cuda_error = 0;
         }                                              \
     } while (0)
 
-__device__ mxdsa::DeviceFault g_fault;
-#ifdef MXDSA_PROFILE
-__device__ unsigned long long g_prof[512];
-#endif
+__device__ mxdsa::DeviceFault g_fault = {0, 0};   // zero at load: the first call needs no memset (and so no implicit synchronisation)
 
 struct DeviceInfo {
     bool ready = false;
@@ -55,7 +52,6 @@ int device_info(DeviceInfo** out) {
             void* sym = nullptr;
             MX_CUDA(cudaGetSymbolAddress(&sym, g_fault));
             d.fault = static_cast<mxdsa::DeviceFault*>(sym);
-            MX_CUDA(cudaMemset(d.fault, 0, sizeof(mxdsa::DeviceFault)));
         }
         if (g_encode == nullptr) {
             cudaDriverEntryPointQueryResult q;
@@ -144,16 +140,6 @@ int launch_pairs(K kernel, int groups, dim3 grid, cudaStream_t stream, const mxd
     attr.val.clusterDim = {2, 1, 1};
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-#ifdef MXDSA_PROFILE
-    {
-        mxdsa::AttnParams ap2 = ap;
-        void* sym = nullptr;
-        MX_CUDA(cudaGetSymbolAddress(&sym, g_prof));
-        ap2.prof = static_cast<unsigned long long*>(sym);
-        MX_CUDA(cudaLaunchKernelEx(&cfg, kernel, ap2, maps));
-        return MXDSA_OK;
-    }
-#endif
     MX_CUDA(cudaLaunchKernelEx(&cfg, kernel, ap, maps));
     return MXDSA_OK;
 }
@@ -328,14 +314,6 @@ int mxdsa_device_fault(void* stream) {
     return MXDSA_OK;
 }
 
-#ifdef MXDSA_PROFILE
-// profiling builds only: copy out the stall counters of cluster 0 ([2][64] cycles)
-int mxdsa_debug_read_prof(unsigned long long* host_out) {
-    MX_CUDA(cudaDeviceSynchronize());
-    MX_CUDA(cudaMemcpyFromSymbol(host_out, g_prof, sizeof(unsigned long long) * 512));
-    return MXDSA_OK;
-}
-#endif
 
 int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     if (p == nullptr || p->q == nullptr || p->kv == nullptr || p->indices == nullptr || p->out == nullptr ||
@@ -525,7 +503,7 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
 extern "C" int mxdsa_decode_combine(const mxdsa_combine_params* p) {
     if (p == nullptr || p->sched_meta == nullptr || p->num_splits == nullptr || p->out == nullptr || p->lse == nullptr)
         return MXDSA_ERR_NULL;
-    if (p->b <= 0 || p->s_q <= 0 || p->num_sm_parts <= 0) return MXDSA_ERR_SHAPE;
+    if (p->b <= 0 || p->s_q <= 0 || p->num_sm_parts <= 0 || p->num_sm_parts > kMaxSplits) return MXDSA_ERR_SHAPE;
     const size_t need = mxdsa_decode_workspace_bytes(p->b, p->s_q, p->num_sm_parts);
     if (p->workspace == nullptr || p->workspace_bytes < need || !aligned32(p->workspace)) return MXDSA_ERR_WORKSPACE;
     if (!aligned32(p->out)) return MXDSA_ERR_ALIGN;

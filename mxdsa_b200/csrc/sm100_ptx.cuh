@@ -1,4 +1,4 @@
-// Thin inline-PTX layer for sm_100a: mbarriers with bounded waits, TMA (tiled, gather4, bulk),
+// Thin inline-PTX layer for sm_100a: mbarriers with bounded waits, TMA gather4,
 // tensor-memory management and tcgen05 block-scaled MMA.  Everything the attention kernels need
 // from the hardware goes through this file; nothing here is specific to attention.
 //
@@ -21,11 +21,6 @@ namespace sm100 {
 
 SM100_DEVICE uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-SM100_DEVICE uint32_t lane_id() {
-    uint32_t v;
-    asm volatile("mov.u32 %0, %%laneid;" : "=r"(v));
-    return v;
 }
 SM100_DEVICE uint32_t cluster_cta_rank() {
     uint32_t v;
@@ -92,21 +87,6 @@ SM100_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Non-blocking test: returns at once (try_wait may hold the thread for a system-dependent time while
-// the phase is pending, which is wrong for a thread that watches two barriers).
-SM100_DEVICE bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
 // Blocking flavour: the hardware may suspend the thread for up to `ns` nanoseconds while the phase
 // is pending, so a waiting warp does not compete for issue slots with the warps doing the work.
 SM100_DEVICE bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns, bool cluster_scope) {
@@ -166,19 +146,9 @@ static constexpr uint64_t kEvictFirst = 0x12F0000000000000ull;
 static constexpr uint64_t kEvictLast = 0x14F0000000000000ull;
 static constexpr uint64_t kEvictNormal = 0x1000000000000000ull;
 
-// Four rows (rows r0..r3 of a 2-D tensor map, box = {box_cols, 1}) starting at column `col`
-// land as four consecutive box rows at `dst`; completion bytes go to `bar` of this CTA.
-SM100_DEVICE void tma_gather4(uint32_t dst, const void* map, int col, int r0, int r1, int r2, int r3,
-                              uint32_t bar, uint64_t hint) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes"
-        ".cta_group::1.L2::cache_hint [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;"
-        :
-        : "r"(dst), "l"(map), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar), "l"(hint)
-        : "memory");
-}
-// Same, but the completion may be routed to a barrier of either CTA of the pair: `bar` is a
-// shared::cluster address (own window address, or the peer's from map_to_cta()).
+// gather4: four rows (r0..r3 of a 2-D tensor map whose box is {box_cols, 1}) starting at column `col` land as four
+// consecutive box rows at `dst`.  The completion bytes may be routed to a barrier of either CTA of the pair:
+// `bar` is a shared::cluster address (own window address, or the peer's from map_to_cta()).
 SM100_DEVICE void tma_gather4_pair(uint32_t dst, const void* map, int col, int r0, int r1, int r2,
                                    int r3, uint32_t bar, uint64_t hint) {
     asm volatile(
@@ -188,60 +158,22 @@ SM100_DEVICE void tma_gather4_pair(uint32_t dst, const void* map, int col, int r
         : "r"(dst), "l"(map), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar), "l"(hint)
         : "memory");
 }
-SM100_DEVICE void tma_load_3d(uint32_t dst, const void* map, int c0, int c1, int c2, uint32_t bar,
-                              uint64_t hint) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%2, %3, %4}], [%5], %6;"
-        :
-        : "r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar), "l"(hint)
-        : "memory");
-}
-SM100_DEVICE void tma_store_3d(const void* map, uint32_t src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 :
-                 : "l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
-SM100_DEVICE void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> SM100_DEVICE void tma_store_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N> SM100_DEVICE void tma_store_wait_all() {
-    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
-// plain bulk copy global -> shared (16-byte aligned, size multiple of 16)
-SM100_DEVICE void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        :
-        : "r"(dst), "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
-}
 
 // ----------------------------------------------------------------------------------------------
 // tensor memory
 // ----------------------------------------------------------------------------------------------
 template <int CG> SM100_DEVICE void tmem_alloc(uint32_t result_smem, uint32_t cols) {
-    if constexpr (CG == 1)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem),
-                     "r"(cols)
-                     : "memory");
-    else
+    static_assert(CG == 2, "only CTA-pair (cta_group::2) operations are used");
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem),
                      "r"(cols)
                      : "memory");
 }
 template <int CG> SM100_DEVICE void tmem_relinquish() {
-    if constexpr (CG == 1)
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    else
+    static_assert(CG == 2, "only CTA-pair (cta_group::2) operations are used");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
 }
 template <int CG> SM100_DEVICE void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    if constexpr (CG == 1)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-    else
+    static_assert(CG == 2, "only CTA-pair (cta_group::2) operations are used");
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 SM100_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -250,33 +182,9 @@ SM100_DEVICE void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;"
 SM100_DEVICE void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // tcgen05.ld/st .32x32b: thread t of the warp accesses lane (warp%4)*32+t, N consecutive columns.
-template <int N> struct TmemVec;
-#define SM100_REGS_1(p, o) "%" #o
-SM100_DEVICE void tmem_ld1(uint32_t addr, uint32_t& v) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(addr));
-}
-SM100_DEVICE void tmem_st1(uint32_t addr, uint32_t v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(addr), "r"(v));
-}
-SM100_DEVICE void tmem_st2(uint32_t addr, uint32_t a, uint32_t b) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b));
-}
-SM100_DEVICE void tmem_st4(uint32_t addr, const uint32_t* v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[0]),
-                 "r"(v[1]), "r"(v[2]), "r"(v[3]));
-}
 SM100_DEVICE void tmem_st8(uint32_t addr, const uint32_t* v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(addr),
                  "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]));
-}
-SM100_DEVICE void tmem_ld16(uint32_t addr, uint32_t* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-          "=r"(v[15])
-        : "r"(addr));
 }
 SM100_DEVICE void tmem_ld32(uint32_t addr, uint32_t* v) {
     asm volatile(
@@ -290,13 +198,6 @@ SM100_DEVICE void tmem_ld32(uint32_t addr, uint32_t* v) {
           "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(addr));
 }
-SM100_DEVICE void tmem_st16(uint32_t addr, const uint32_t* v) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(addr),
-        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]));
-}
 SM100_DEVICE void tmem_st32(uint32_t addr, const uint32_t* v) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -309,15 +210,9 @@ SM100_DEVICE void tmem_st32(uint32_t addr, const uint32_t* v) {
 }
 
 // shared -> tensor memory copy of scale-factor rows (16 bytes per row).
-//  pair form:   64 rows; rows 0-31 go to lane quadrants 0 and 1, rows 32-63 to quadrants 2 and 3,
-//               in both CTAs of the pair.
-//  single form: 32 rows, replicated into all four lane quadrants of this CTA.
+// 64 rows; rows 0-31 go to lane quadrants 0 and 1, rows 32-63 to quadrants 2 and 3, in both CTAs of the pair.
 SM100_DEVICE void tmem_cp_sf_pair(uint32_t tmem_addr, uint64_t smem_desc) {
     asm volatile("tcgen05.cp.cta_group::2.64x128b.warpx2::01_23 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc)
-                 : "memory");
-}
-SM100_DEVICE void tmem_cp_sf_single(uint32_t tmem_addr, uint64_t smem_desc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc)
                  : "memory");
 }
 
@@ -342,16 +237,7 @@ SM100_DEVICE constexpr uint32_t mx_idesc(uint32_t m, uint32_t n, bool b_mn_major
 template <int CG>
 SM100_DEVICE void mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                            uint32_t sfa_tmem, uint32_t sfb_tmem, bool accumulate) {
-    if constexpr (CG == 1)
-        asm volatile(
-            "{\n"
-            ".reg .pred p;\n"
-            "setp.ne.b32 p, %4, 0;\n"
-            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
-            "}\n" ::"r"(d_tmem),
-            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate)), "r"(sfa_tmem), "r"(sfb_tmem)
-            : "memory");
-    else
+    static_assert(CG == 2, "only CTA-pair (cta_group::2) operations are used");
         asm volatile(
             "{\n"
             ".reg .pred p;\n"
@@ -364,10 +250,7 @@ SM100_DEVICE void mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, ui
 // Arrive on an mbarrier once every tcgen05 operation issued so far by this thread has finished.
 // `bar` is a shared::cluster address, so the peer's barrier can be targeted through map_to_cta().
 template <int CG> SM100_DEVICE void mma_commit(uint32_t bar) {
-    if constexpr (CG == 1)
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                     : "memory");
-    else
+    static_assert(CG == 2, "only CTA-pair (cta_group::2) operations are used");
         asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                      : "memory");
 }
@@ -402,10 +285,6 @@ SM100_DEVICE uint32_t cvt_ue8m0_roundup(float x) {
 // to 1024 bytes (16-byte chunk index XOR row-in-group-of-8).
 SM100_DEVICE constexpr uint32_t swz128(uint32_t row, uint32_t byte_in_row) {
     return row * 128u + ((((byte_in_row >> 4) ^ (row & 7u)) << 4) | (byte_in_row & 15u));
-}
-// 64-byte swizzle: rows of 64 bytes, pattern repeats every 512 bytes.
-SM100_DEVICE constexpr uint32_t swz64(uint32_t row, uint32_t byte_in_row) {
-    return row * 64u + ((((byte_in_row >> 4) ^ ((row >> 1) & 3u)) << 4) | (byte_in_row & 15u));
 }
 
 }  // namespace sm100
