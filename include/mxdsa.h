@@ -173,6 +173,15 @@ typedef struct mxdsa_combine_params {
 } mxdsa_combine_params;
 int mxdsa_decode_combine(const mxdsa_combine_params* p);
 
+/* Self-test of the kernels' bounded waits.  (No counterpart in the reference, whose kernels trap or spin.)
+ * Launches a two-CTA kernel that waits -- with the attention kernel's own wait loops, limits turned down to
+ * about a millisecond -- on a barrier nobody arrives on, gives up, raises the device fault record and leaves
+ * through its normal tear-down.  Nothing faults or hangs.  Afterwards mxdsa_device_fault(stream) returns
+ * MXDSA_ERR_DEVICE_TIMEOUT once and clears the record.  mxdsa_selftest_teardowns() synchronises the stream
+ * and returns how many self-test CTAs have reached their tear-down since the library was loaded. */
+int mxdsa_selftest_bounded_wait(void* stream);
+int mxdsa_selftest_teardowns(void* stream);
+
 /* Decode without caller-provided scratch.  (No counterpart in the reference, whose binding
  * allocates its scratch with torch on every call.)
  *

@@ -30,6 +30,8 @@ thread_local int tl_last_cuda_error = 0;
 
 __device__ mxdsa::DeviceFault g_fault = {0, 0};   // zero at load: the first call needs no memset (and so no implicit synchronisation)
 
+__device__ int g_selftest_teardowns = 0;
+
 struct DeviceInfo {
     bool ready = false;
     int major = 0, sm_count = 0;
@@ -314,6 +316,35 @@ int mxdsa_device_fault(void* stream) {
     return MXDSA_OK;
 }
 
+
+// Runs the bounded-wait self-test kernel (attn_sm100.cuh) on `stream`.  Afterwards mxdsa_device_fault(stream)
+// reports MXDSA_ERR_DEVICE_TIMEOUT once and clears the record; the context stays usable.
+int mxdsa_selftest_bounded_wait(void* stream) {
+    DeviceInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MXDSA_OK) return st;
+    void* counter = nullptr;
+    MX_CUDA(cudaGetSymbolAddress(&counter, g_selftest_teardowns));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2);
+    cfg.blockDim = dim3(64);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim = {2, 1, 1};
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    MX_CUDA(cudaLaunchKernelEx(&cfg, mxdsa::mxdsa_wait_selftest_kernel, d->fault, static_cast<int*>(counter)));
+    return MXDSA_OK;
+}
+
+// Number of CTAs of the self-test that have left through their tear-down since the library was loaded.
+int mxdsa_selftest_teardowns(void* stream) {
+    MX_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    int n = 0;
+    MX_CUDA(cudaMemcpyFromSymbol(&n, g_selftest_teardowns, sizeof(int)));
+    return n;
+}
 
 int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     if (p == nullptr || p->q == nullptr || p->kv == nullptr || p->indices == nullptr || p->out == nullptr ||

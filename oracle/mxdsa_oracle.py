@@ -24,9 +24,12 @@ PARITY PIN.  The reference ships no golden vectors or known-answer tests, and it
 path.  The pin is therefore the reference's own kernels, compiled unmodified by
 ``oracle/build_ref.sh`` and run on a B200 by ``tests/golden/gen_golden.py``; the inputs and the
 reference outputs of those runs are committed under ``tests/golden/`` and
-``tests/test_oracle_golden.py`` checks this oracle against them.  The integer parts (packing,
-scheduler metadata) are additionally cross-checked bit-for-bit against the reference's Python
-packers and scheduler kernel through the same fixtures.
+``tests/test_oracle_golden.py`` checks this oracle against them.  The integer parts are pinned
+bit for bit as well: the packers against the bytes of the reference's own Python packers
+(``tests/golden/packers.npz``, written by ``tests/golden/gen_packer_golden.py`` from the
+unmodified ``tests/mxfp8_test_utils.py`` of the reference; checked by
+``tests/test_packers_reference_pin.py``), the scheduler metadata against the records of the
+reference's scheduler kernel in the same golden fixtures.
 
 Two levels of fidelity:
   level 0  exact softmax attention on the de-quantised operands in float64 (the ideal the kernel
@@ -432,7 +435,9 @@ def _decode_row_keys(r, row, indices, topk_length, kvd, extra_indices, extra_top
     idx = np.full(nblk * 64, -1, dtype=np.int64)
     m = min(topk, nblk * 64)
     idx[:m] = indices[r, row, :m]
-    valid = (idx != -1) & (pos < n)                   # decode_kernel.cuh:666-669
+    # decode_kernel.cuh:666-669 attends every index != -1.  An index outside the pool is undefined behaviour
+    # there (the scale slot is read out of bounds); the library under test skips such a key, and so does this.
+    valid = (idx >= 0) & (idx < data.shape[0]) & (pos < n)
     safe = np.where(valid, idx, 0)
     d_rows, s_rows = data[safe], slots[safe]
     if ekvd is not None and extra_indices is not None and extra_indices.shape[-1] > 0:
@@ -444,7 +449,7 @@ def _decode_row_keys(r, row, indices, topk_length, kvd, extra_indices, extra_top
         eidx = np.full(enblk * 64, -1, dtype=np.int64)
         em = min(etopk, enblk * 64)
         eidx[:em] = extra_indices[r, row, :em]
-        evalid = (eidx != -1) & (epos < en)
+        evalid = (eidx >= 0) & (eidx < edata.shape[0]) & (epos < en)
         esafe = np.where(evalid, eidx, 0)
         d_rows = np.concatenate([d_rows, edata[esafe]])
         s_rows = np.concatenate([s_rows, eslots[esafe]])

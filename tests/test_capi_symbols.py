@@ -60,6 +60,10 @@ def test_status_strings_and_argument_checks_need_no_gpu():
     assert L.mxdsa_pack_kv(ctypes.byref(k)) == 2         # rows not a multiple of the page size
     k = capi.PackKVParams(rows=8, src=16, src_dtype=capi.DTYPE_BF16, dst=16, rows_per_page=0)
     assert L.mxdsa_pack_kv(ctypes.byref(k)) == 2
+    # the combine step on its own keeps its per-warp weights in a fixed shared array of 192 splits
+    c = capi.CombineParams(b=4, s_q=1, num_sm_parts=193, sched_meta=16, num_splits=16, workspace=32,
+                           workspace_bytes=1 << 30, out=32, lse=16)
+    assert L.mxdsa_decode_combine(ctypes.byref(c)) == 2   # more parts than the kernel can merge -> MXDSA_ERR_SHAPE
 
 
 def test_extension_module_exposes_the_reference_entry_points():

@@ -70,6 +70,20 @@ def test_pack_decode_pages_matches_oracle():
     assert np.array_equal(got.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cuda_packers_equal_reference_bytes(dtype):
+    """The fused kernels against the bytes of the reference's own Python packers (tests/golden/packers.npz)."""
+    import os
+    import packer_cases as PC
+    from helpers import GOLDEN_DIR
+    from mxdsa_b200 import quantize as Z
+    g = np.load(os.path.join(GOLDEN_DIR, "packers.npz"))
+    cuda = lambda a: torch.from_numpy(a).to("cuda", dtype)
+    assert np.array_equal(Z.pack_dual_q64(cuda(PC.q_input())).cpu().numpy(), g["q"])
+    assert np.array_equal(Z.pack_dual_prefill_kv64(cuda(PC.prefill_kv_input())).cpu().numpy(), g["prefill_kv"])
+    assert np.array_equal(Z.pack_dual_decode_kv_pages(cuda(PC.decode_kv_input())).cpu().numpy(), g["decode_kv"])
+
+
 def test_packed_tensors_feed_the_attention_entry_point():
     """End of the widened path: fused packers -> prefill attention equals torch packers -> prefill attention."""
     import mxdsa_b200 as M
