@@ -182,6 +182,12 @@ int mxdsa_decode_combine(const mxdsa_combine_params* p);
 int mxdsa_selftest_bounded_wait(void* stream);
 int mxdsa_selftest_teardowns(void* stream);
 
+/* Issue-only tensor-core rate probe.  (No counterpart in the reference.)  Every CTA pair of the device issues
+ * `iters` batches of 64 block-scaled E4M3 MMAs (tcgen05 kind::mxf8f6f4, cta_group::2) of shape M128 x N`n` x K32
+ * (n = 128: the QK shape, n = 256: the PV shape) on 64 KB of operand bytes copied from `data`.  The caller times
+ * the launch: flops = (SMs / 2) * iters * 64 * 2 * 128 * n * 32.  Used as the measured MXFP8 roof. */
+int mxdsa_selftest_mma_rate(const void* data, int n, int iters, void* stream);
+
 /* Decode without caller-provided scratch.  (No counterpart in the reference, whose binding
  * allocates its scratch with torch on every call.)
  *

@@ -15,7 +15,7 @@ EXPORTS = (
     "mxdsa_status_string", "mxdsa_last_cuda_error", "mxdsa_device_fault", "mxdsa_prefill_fwd",
     "mxdsa_num_sm_parts", "mxdsa_decode_sched", "mxdsa_decode_workspace_bytes", "mxdsa_decode_fwd",
     "mxdsa_decode_fwd_static", "mxdsa_decode_combine", "mxdsa_pack_q", "mxdsa_pack_kv", "mxdsa_pack_last_cuda_error",
-    "mxdsa_topk_select", "mxdsa_topk_last_cuda_error", "mxdsa_selftest_bounded_wait", "mxdsa_selftest_teardowns",
+    "mxdsa_topk_select", "mxdsa_topk_last_cuda_error", "mxdsa_selftest_bounded_wait", "mxdsa_selftest_teardowns", "mxdsa_selftest_mma_rate",
 )
 DTYPE_BF16, DTYPE_F32 = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
@@ -119,6 +119,7 @@ def lib() -> C.CDLL:
         L.mxdsa_topk_last_cuda_error.restype = C.c_int
         L.mxdsa_selftest_bounded_wait.argtypes = [C.c_void_p]
         L.mxdsa_selftest_teardowns.argtypes = [C.c_void_p]
+        L.mxdsa_selftest_mma_rate.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         _lib = L
     return _lib
 

@@ -1273,4 +1273,87 @@ done:
     if (threadIdx.x == 0) atomicAdd(reached_teardown, 1);
 }
 
+// ----------------------------------------------------------------------------------------------
+// Issue-only tensor-core rate probe: what the block-scaled E4M3 MMA of this library's shapes can do when
+// nothing else is in the way.  A CTA pair keeps issuing cta_group::2 kind::mxf8f6f4 MMAs (M = 128, K = 32,
+// N = `n` of 128 or 256) on operand bytes that sit in shared memory (copied once from `data`, so that the
+// multipliers see real bit patterns, not zeros), accumulating into tensor memory; a commit and a bounded wait
+// every 64 instructions keep the queue shallow.  Flops = pairs x iters x 64 x 2 x 128 x n x 32.
+// The roofline fractions of the attention kernel are quoted against this number beside 2 x the bf16 GEMM rate.
+// ----------------------------------------------------------------------------------------------
+struct MmaRatePlan {
+    uint64_t bar_done;
+    uint32_t tmem_base;
+    int abort_word;
+    DeviceFault* fault;
+};
+__global__ void __launch_bounds__(128, 1) mxdsa_mma_rate_kernel(const uint4* data, int n, int iters, DeviceFault* fault) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 64 KB of operands, then the plan
+    MmaRatePlan& sm = *reinterpret_cast<MmaRatePlan*>(tiles + 65536);
+    const int warp = threadIdx.x / 32;
+    const uint32_t cta = cluster_cta_rank();
+    for (int i = threadIdx.x; i < 65536 / 16; i += blockDim.x) reinterpret_cast<uint4*>(tiles)[i] = __ldg(data + i);
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&sm.bar_done), 1);
+        sm.abort_word = 0;
+        sm.fault = fault;
+        fence_mbar_init();
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 0) {
+        tmem_alloc<2>(smem_u32(&sm.tmem_base), 512);
+        tmem_relinquish<2>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    if (warp == 1 && cta == 0) {
+        const uint64_t desc_k = smem_desc_base(16, 1024, 2), desc_v = smem_desc_base(16384, 1024, 2);
+        const uint64_t a_base = smem_desc(desc_k, smem_u32(tiles));               // [4 chunks][64 rows][128 B]
+        const uint64_t b_k = smem_desc(desc_k, smem_u32(tiles + 32768));          // K-like operand (N = 128)
+        const uint64_t b_v = smem_desc(desc_v, smem_u32(tiles + 32768));          // V-like operand (N = 256)
+        const uint32_t peer_done = map_to_cta(smem_u32(&sm.bar_done), 1);
+        constexpr int kBatch = 16;
+#pragma unroll 1
+        for (int it = 0; it < iters; ++it) {
+            __syncwarp();
+            if (elect_one()) {
+#pragma unroll 1
+              for (int rep = 0; rep < 4; ++rep) {      // four batches of 16 per commit: the wait is amortised over 64 instructions
+                if (n == 128) {
+#pragma unroll
+                    for (int kk = 0; kk < kBatch; ++kk) {
+                        const uint32_t a_off = ((kk & 7) >> 1) * 8192 + (kk & 1) * 64 + (kk >> 3) * 32;
+                        const uint32_t b_off = (kk >> 2) * 8192 + (kk & 3) * 32;
+                        mma_mxf8<2>(tmem + 256 + (kk & 1) * 64, a_base + (a_off >> 4), b_k + (b_off >> 4),
+                                    mx_idesc(128, 128, false, kk & 3, (kk >> 1) & 3), tmem + 448, tmem + 456, true);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kBatch; ++i) {
+                        const int ks = (i >> 1) & 3, c = i & 1;
+                        mma_mxf8<2>(tmem + c * 128, a_base + ((ks * 32) >> 4), b_v + ((c * 16384 + ks * 4096) >> 4),
+                                    mx_idesc(128, 256, true, ks, ks), tmem + 448, tmem + 456, true);
+                    }
+                }
+              }
+                mma_commit<2>(smem_u32(&sm.bar_done));
+                (void)peer_done;
+            }
+            __syncwarp();
+            MXDSA_WAIT_LIMITED_(0, smem_u32(&sm.bar_done), it & 1, 92, 24, 8);
+        }
+    }
+done:
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 0) tmem_dealloc<2>(tmem, 512);
+}
+
 }  // namespace mxdsa

@@ -338,6 +338,32 @@ int mxdsa_selftest_bounded_wait(void* stream) {
     return MXDSA_OK;
 }
 
+// Launches the issue-only tensor-core rate probe (attn_sm100.cuh) on every CTA pair of the device: `iters` batches
+// of 64 block-scaled E4M3 MMAs of shape M128 x N`n` x K32 per pair.  `data` = at least 64 KB of operand bytes.
+// The caller times the launch; flops = (SMs / 2) * iters * 64 * 2 * 128 * n * 32.
+int mxdsa_selftest_mma_rate(const void* data, int n, int iters, void* stream) {
+    if (data == nullptr) return MXDSA_ERR_NULL;
+    if ((n != 128 && n != 256) || iters <= 0) return MXDSA_ERR_SHAPE;
+    if (!aligned16(data)) return MXDSA_ERR_ALIGN;
+    DeviceInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MXDSA_OK) return st;
+    const int smem = 65536 + 1024 + 256;
+    MX_CUDA(cudaFuncSetAttribute(mxdsa::mxdsa_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (d->sm_count / 2));
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim = {2, 1, 1};
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    MX_CUDA(cudaLaunchKernelEx(&cfg, mxdsa::mxdsa_mma_rate_kernel, static_cast<const uint4*>(data), n, iters, d->fault));
+    return MXDSA_OK;
+}
+
 // Number of CTAs of the self-test that have left through their tear-down since the library was loaded.
 int mxdsa_selftest_teardowns(void* stream) {
     MX_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
