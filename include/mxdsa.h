@@ -62,8 +62,11 @@ int mxdsa_device_fault(void* stream);
  *
  * Query tokens 2p and 2p+1 share index row p.  Key j of row p is attended when
  * 0 <= indices[p][j] < s_kv and j < topk_length[p] (topk when topk_length is NULL).
- * Rules: s_q > 0 and even; topk > 0 and a multiple of 64; q, kv 16-byte aligned; out 32-byte
- * aligned; stride_q_token a multiple of 16 bytes.
+ * Rules: s_q > 0; topk > 0; q, kv 16-byte aligned; out 32-byte aligned; stride_q_token a multiple
+ * of 16 bytes.  The reference operator additionally demands an even s_q and topk % 64 == 0
+ * (binding.cpp:36-45); those two rules live in the operator layer above this call, so that the
+ * same entry point also serves an odd s_q (ceil(s_q/2) index rows, the last one used by one
+ * token) and any topk (positions >= topk are not attended; tiles of 128 keys from topk 512 on).
  * ------------------------------------------------------------------------------------------ */
 typedef struct mxdsa_prefill_params {
     int32_t s_q, s_kv, topk;
@@ -71,10 +74,10 @@ typedef struct mxdsa_prefill_params {
     const void* q;               /* u8 [s_q][64][528]                                   */
     int64_t stride_q_token;      /* bytes between query tokens (>= 64*528)              */
     const void* kv;              /* u8 flat: s_kv*512 data bytes, then s_kv*16 slots    */
-    const int32_t* indices;      /* [s_q/2][topk]                                       */
+    const int32_t* indices;      /* [ceil(s_q/2)][topk]                                 */
     int64_t stride_indices_pair; /* elements between index rows                         */
     const float* attn_sink;      /* [64] or NULL                                        */
-    const int32_t* topk_length;  /* [s_q/2] or NULL                                     */
+    const int32_t* topk_length;  /* [ceil(s_q/2)] or NULL                               */
     uint32_t w1[8], w2[8];
     void* out;                   /* bf16 [s_q][64][512]                                 */
     float* max_logits;           /* [s_q][64]  max of sm_scale*logit, -inf if no key    */

@@ -44,6 +44,13 @@ def dual_mxfp8_head64_sparse_prefill_fwd(q, kv, indices, sm_scale, w1, w2, attn_
                                                       topk_length)
 
 
+def dual_mxfp8_head64_sparse_prefill_fwd_ex(q, kv, indices, sm_scale, w1, w2, attn_sink=None, topk_length=None):
+    """The prefill operator with an odd number of query tokens, any positive topk and float8_e4m3fn inputs allowed
+    (no counterpart in the reference; indices [ceil(s_q/2), 1, topk])."""
+    return ext().dual_mxfp8_head64_sparse_prefill_fwd_ex(q, kv, indices, sm_scale, list(w1), list(w2), attn_sink,
+                                                         topk_length)
+
+
 def dual_mxfp8_sparse_decode_fwd(q, kv, indices, topk_length, attn_sink, tile_scheduler_metadata, num_splits,
                                  extra_kv, extra_indices, extra_topk_length, d_qk, d_v, sm_scale, w1, w2):
     return ext().dual_mxfp8_sparse_decode_fwd(q, kv, indices, topk_length, attn_sink, tile_scheduler_metadata,
@@ -56,5 +63,6 @@ def device_fault() -> None:
     ext().device_fault()
 
 
-__all__ = ["dual_mxfp8_head64_sparse_prefill_fwd", "dual_mxfp8_sparse_decode_fwd", "device_fault", "ext", "api",
+__all__ = ["dual_mxfp8_head64_sparse_prefill_fwd", "dual_mxfp8_head64_sparse_prefill_fwd_ex",
+           "dual_mxfp8_sparse_decode_fwd", "device_fault", "ext", "api",
            "capi", "packing"]

@@ -53,30 +53,46 @@ def dual_mxfp8_head64_sparse_prefill_fwd(q: torch.Tensor, kv: torch.Tensor, indi
     """Sparse MXFP8 prefill attention.  q u8 [s_q,64,528], kv u8 [s_kv,1,528] (contiguous
     envelope), indices i32 [s_q/2,1,topk]; returns [out bf16 [s_q,64,512], max_logits f32 [s_q,64],
     lse f32 [s_q,64]].  Does not synchronise."""
+    return _prefill(q, kv, indices, sm_scale, w1, w2, attn_sink, topk_length, extended=False)
+
+
+def dual_mxfp8_head64_sparse_prefill_fwd_ex(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
+                                            sm_scale: float, w1: Sequence[int], w2: Sequence[int],
+                                            attn_sink: Optional[torch.Tensor] = None,
+                                            topk_length: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+    """The prefill operator without three restrictions of the reference's (which has no counterpart of
+    this entry point): s_q may be odd (indices [ceil(s_q/2),1,topk]; the last pair then has one token),
+    topk may be any positive number, and q / kv may be torch.float8_e4m3fn as well as uint8."""
+    return _prefill(q, kv, indices, sm_scale, w1, w2, attn_sink, topk_length, extended=True)
+
+
+def _prefill(q, kv, indices, sm_scale, w1, w2, attn_sink, topk_length, extended: bool) -> List[torch.Tensor]:
     _req(q.dim() == 3, "q must have 3 dimensions")
     _req(kv.dim() == 3, "kv must have 3 dimensions")
     _req(indices.dim() == 3, "indices must have 3 dimensions")
     s_q, h_q = q.size(0), q.size(1)
     s_kv, h_kv = kv.size(0), kv.size(1)
     topk = indices.size(2)
-    _req(s_q > 0 and s_q % 2 == 0, "q must contain an even, positive number of query tokens")
+    _req(s_q > 0 and (extended or s_q % 2 == 0), "q must contain an even, positive number of query tokens")
+    pairs = (s_q + 1) // 2
     _req(h_q == HEADS, "q must have shape [s_q, 64, 528]")
     _req(h_kv == 1, "kv must have shape [s_kv, 1, 528]")
     _req(q.size(2) == ROW, "q must store 512 E4M3 bytes followed by a replicated 16-byte UE8M0 scale slot per head")
     _req(kv.size(2) == ROW, "kv must provide a 528-byte envelope per token for replicated page-tail scales")
-    _req(topk > 0 and topk % 64 == 0, "topk must be a positive multiple of 64")
+    _req(topk > 0 and (extended or topk % 64 == 0), "topk must be a positive multiple of 64")
     w1c, w2c = _words(w1, "w1"), _words(w2, "w2")
     for t, n in ((q, "q"), (kv, "kv"), (indices, "indices")):
         _req(t.is_cuda, f"{n} must be on CUDA")
-    _req(q.dtype == torch.uint8, "q must have dtype torch.uint8")
-    _req(kv.dtype == torch.uint8, "kv must have dtype torch.uint8")
+    bytes_ok = (torch.uint8, torch.float8_e4m3fn) if extended else (torch.uint8,)
+    _req(q.dtype in bytes_ok, "q must have dtype torch.uint8")
+    _req(kv.dtype in bytes_ok, "kv must have dtype torch.uint8")
     _req(indices.dtype == torch.int32, "indices must have dtype torch.int32")
     _req(q.stride(-1) == 1, "q must have contiguous last dimension")
     _req(kv.is_contiguous(), "kv must be contiguous")
     _req(indices.stride(-1) == 1, "indices must have contiguous last dimension")
-    _req(tuple(indices.shape) == (s_q // 2, 1, topk), "indices must have shape (num_q_pairs, h_kv, topk)")
+    _req(tuple(indices.shape) == (pairs, 1, topk), "indices must have shape (num_q_pairs, h_kv, topk)")
     _check_opt(attn_sink, "attn_sink", torch.float32, (HEADS,))
-    _check_opt(topk_length, "topk_length", torch.int32, (s_q // 2,))
+    _check_opt(topk_length, "topk_length", torch.int32, (pairs,))
     _req(q.stride(1) == ROW, "Q head stride must be 512 e4m3 bytes + an aligned 16-byte scale slot")
     for t in (q, indices):
         for st in t.stride():

@@ -376,7 +376,7 @@ int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     if (p == nullptr || p->q == nullptr || p->kv == nullptr || p->indices == nullptr || p->out == nullptr ||
         p->max_logits == nullptr || p->lse == nullptr)
         return MXDSA_ERR_NULL;
-    if (p->s_q <= 0 || (p->s_q & 1) || p->s_kv <= 0 || p->topk <= 0 || (p->topk % 64) != 0) return MXDSA_ERR_SHAPE;
+    if (p->s_q <= 0 || p->s_kv <= 0 || p->topk <= 0) return MXDSA_ERR_SHAPE;
     if (p->stride_q_token < (int64_t)MXDSA_HEADS * MXDSA_ROW_BYTES || p->stride_indices_pair < p->topk)
         return MXDSA_ERR_SHAPE;
     if (!aligned16(p->q) || !aligned16(p->kv) || (p->stride_q_token & 15) || !aligned32(p->out))
@@ -404,7 +404,7 @@ int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     memcpy(ap.w2, p->w2, sizeof(ap.w2));
     ap.fault = d->fault;
     ap.s_kv = p->s_kv;
-    ap.num_pairs = p->s_q / 2;
+    ap.num_pairs = (p->s_q + 1) / 2;   // the last pair of an odd batch has one token: its second half is computed on a repeated row and not stored
     ap.kv = static_cast<const uint8_t*>(p->kv);
     ap.kv_scales = static_cast<const uint8_t*>(p->kv) + (size_t)p->s_kv * MXDSA_DIM;
     ap.b = 1;

@@ -56,36 +56,45 @@ bool is_e4m3_storage(const at::Tensor& t) {
     return t.scalar_type() == at::kByte || t.scalar_type() == at::kFloat8_e4m3fn;
 }
 
-std::vector<at::Tensor> prefill_fwd(const at::Tensor& q, const at::Tensor& kv, const at::Tensor& indices,
-                                    double sm_scale, const std::vector<uint32_t>& w1,
-                                    const std::vector<uint32_t>& w2, const OptTensor& attn_sink,
-                                    const OptTensor& topk_length) {
+// `extended` = false: the reference operator's rules to the letter (csrc/bindings/binding.cpp:36-71).
+// `extended` = true: the same operator without three of its restrictions -- an odd number of query tokens (the last
+// pair has one token; indices [ceil(s_q/2), 1, topk]), any positive topk (positions beyond it count as not attended,
+// tiles of 128 keys from topk 512 on as in the reference), and torch.float8_e4m3fn as well as uint8 for q / kv (the
+// bytes are the same; the decode operator of the reference already accepts both).
+std::vector<at::Tensor> prefill_impl(const at::Tensor& q, const at::Tensor& kv, const at::Tensor& indices,
+                                     double sm_scale, const std::vector<uint32_t>& w1,
+                                     const std::vector<uint32_t>& w2, const OptTensor& attn_sink,
+                                     const OptTensor& topk_length, bool extended) {
     TORCH_CHECK(q.dim() == 3, "q must have 3 dimensions");
     TORCH_CHECK(kv.dim() == 3, "kv must have 3 dimensions");
     TORCH_CHECK(indices.dim() == 3, "indices must have 3 dimensions");
     const int64_t s_q = q.size(0), h_q = q.size(1), s_kv = kv.size(0), h_kv = kv.size(1), topk = indices.size(2);
-    TORCH_CHECK(s_q > 0 && s_q % 2 == 0, "q must contain an even, positive number of query tokens");
+    TORCH_CHECK(s_q > 0 && (extended || s_q % 2 == 0), "q must contain an even, positive number of query tokens");
+    const int64_t pairs = (s_q + 1) / 2;
     TORCH_CHECK(h_q == kHeads, "q must have shape [s_q, 64, 528]");
     TORCH_CHECK(h_kv == 1, "kv must have shape [s_kv, 1, 528]");
     TORCH_CHECK(q.size(2) == kRow,
                 "q must store 512 E4M3 bytes followed by a replicated 16-byte UE8M0 scale slot per head");
     TORCH_CHECK(kv.size(2) == kRow, "kv must provide a 528-byte envelope per token for replicated page-tail scales");
-    TORCH_CHECK(topk > 0 && topk % 64 == 0, "topk must be a positive multiple of 64");
+    TORCH_CHECK(topk > 0 && (extended || topk % 64 == 0), "topk must be a positive multiple of 64");
     mxdsa_prefill_params p{};
     copy_words(w1, w2, p.w1, p.w2);
     TORCH_CHECK(q.is_cuda(), "q must be on CUDA");
     TORCH_CHECK(kv.is_cuda(), "kv must be on CUDA");
     TORCH_CHECK(indices.is_cuda(), "indices must be on CUDA");
-    TORCH_CHECK(q.scalar_type() == at::kByte, "q must have dtype torch.uint8");
-    TORCH_CHECK(kv.scalar_type() == at::kByte, "kv must have dtype torch.uint8");
+    const bool fp8_ok = extended;
+    TORCH_CHECK(q.scalar_type() == at::kByte || (fp8_ok && q.scalar_type() == at::kFloat8_e4m3fn),
+                "q must have dtype torch.uint8");
+    TORCH_CHECK(kv.scalar_type() == at::kByte || (fp8_ok && kv.scalar_type() == at::kFloat8_e4m3fn),
+                "kv must have dtype torch.uint8");
     TORCH_CHECK(indices.scalar_type() == at::kInt, "indices must have dtype torch.int32");
     TORCH_CHECK(q.stride(-1) == 1, "q must have contiguous last dimension");
     TORCH_CHECK(kv.is_contiguous(), "kv must be contiguous");
     TORCH_CHECK(indices.stride(-1) == 1, "indices must have contiguous last dimension");
-    TORCH_CHECK(indices.sizes() == at::IntArrayRef({s_q / 2, 1, topk}),
+    TORCH_CHECK(indices.sizes() == at::IntArrayRef({pairs, 1, topk}),
                 "indices must have shape (num_q_pairs, h_kv, topk)");
     check_optional(attn_sink, "attn_sink", at::kFloat, {kHeads});
-    check_optional(topk_length, "topk_length", at::kInt, {s_q / 2});
+    check_optional(topk_length, "topk_length", at::kInt, {pairs});
     TORCH_CHECK(q.stride(1) == kRow, "Q head stride must be 512 e4m3 bytes + an aligned 16-byte scale slot");
     for (int64_t st : q.strides()) TORCH_CHECK(st <= INT32_MAX, "Stride exceeds int32 limit: ", st);
     for (int64_t st : indices.strides()) TORCH_CHECK(st <= INT32_MAX, "Stride exceeds int32 limit: ", st);
@@ -114,6 +123,17 @@ std::vector<at::Tensor> prefill_fwd(const at::Tensor& q, const at::Tensor& kv, c
     p.stream = at::cuda::getCurrentCUDAStream().stream();
     require_status(mxdsa_prefill_fwd(&p), "mxdsa_prefill_fwd");
     return {out, max_logits, lse};
+}
+
+std::vector<at::Tensor> prefill_fwd(const at::Tensor& q, const at::Tensor& kv, const at::Tensor& indices, double sm_scale,
+                                    const std::vector<uint32_t>& w1, const std::vector<uint32_t>& w2,
+                                    const OptTensor& attn_sink, const OptTensor& topk_length) {
+    return prefill_impl(q, kv, indices, sm_scale, w1, w2, attn_sink, topk_length, false);
+}
+std::vector<at::Tensor> prefill_fwd_ex(const at::Tensor& q, const at::Tensor& kv, const at::Tensor& indices,
+                                       double sm_scale, const std::vector<uint32_t>& w1, const std::vector<uint32_t>& w2,
+                                       const OptTensor& attn_sink, const OptTensor& topk_length) {
+    return prefill_impl(q, kv, indices, sm_scale, w1, w2, attn_sink, topk_length, true);
 }
 
 std::tuple<at::Tensor, at::Tensor, OptTensor, OptTensor> decode_fwd(
@@ -250,6 +270,7 @@ void device_fault() {
 
 static void define_module(pybind11::module_& m) {
     m.def("dual_mxfp8_head64_sparse_prefill_fwd", &prefill_fwd);
+    m.def("dual_mxfp8_head64_sparse_prefill_fwd_ex", &prefill_fwd_ex);
     m.def("dual_mxfp8_sparse_decode_fwd", &decode_fwd);
     m.def("device_fault", &device_fault);
 }

@@ -370,7 +370,12 @@ def prefill_ref(q_u8: np.ndarray, kv_u8: np.ndarray, indices: np.ndarray, sm_sca
                 topk_length: Optional[np.ndarray] = None, level: int = 1):
     """Restatement of ``dual_mxfp8_head64_sparse_prefill_fwd`` (csrc/bindings/binding.cpp:12-113).
     q_u8 [s_q,64,528], kv_u8 [s_kv,1,528] (flat envelope), indices [s_q/2,1,topk] int32.
-    Returns (out [s_q,64,512] float32 rounded to bf16, max_logits [s_q,64] f32, lse [s_q,64] f32)."""
+    Returns (out [s_q,64,512] float32 rounded to bf16, max_logits [s_q,64] f32, lse [s_q,64] f32).
+    The reference demands an even s_q (binding.cpp:36); an odd one is taken here as "the last index row
+    serves one token" (indices [ceil(s_q/2),1,topk]): the token is evaluated twice and one copy dropped."""
+    s_q_given = q_u8.shape[0]
+    if s_q_given % 2:
+        q_u8 = np.concatenate([q_u8, q_u8[-1:]])
     s_q = q_u8.shape[0]
     s_kv = kv_u8.shape[0]
     topk = indices.shape[-1]
@@ -409,7 +414,7 @@ def prefill_ref(q_u8: np.ndarray, kv_u8: np.ndarray, indices: np.ndarray, sm_sca
         out[2 * p:2 * p + 2] = bf16_round(o.reshape(2, 64, D))
         mxl[2 * p:2 * p + 2] = m.reshape(2, 64)
         lse[2 * p:2 * p + 2] = l.reshape(2, 64)
-    return out, mxl, lse
+    return out[:s_q_given], mxl[:s_q_given], lse[:s_q_given]
 
 
 def _pool_views(pool_u8: np.ndarray):

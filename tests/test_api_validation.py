@@ -33,6 +33,21 @@ def test_prefill_shape_rules(impl, kwargs, needle):
 
 
 @pytest.mark.parametrize("impl", _impls(), ids=["extension", "ctypes"])
+def test_extended_prefill_lifts_three_rules_and_keeps_the_rest(impl):
+    """Odd s_q, any topk and float8_e4m3fn pass the extended operator's checks (it then stops at the first rule
+    both operators share that a CPU tensor breaks); the drop-in operator still refuses float8 inputs."""
+    q = torch.zeros(3, 64, 528, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    kv = torch.zeros(8, 1, 528, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    idx = torch.zeros(2, 1, 100, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="must be on CUDA"):
+        impl.dual_mxfp8_head64_sparse_prefill_fwd_ex(q, kv, idx, 1.0, W, W, None, None)
+    with pytest.raises(RuntimeError, match="(?s).*512 E4M3 bytes"):
+        impl.dual_mxfp8_head64_sparse_prefill_fwd_ex(q[:, :, :512], kv, idx, 1.0, W, W, None, None)
+    with pytest.raises(RuntimeError, match="(?s).*even, positive"):
+        impl.dual_mxfp8_head64_sparse_prefill_fwd(q.view(torch.uint8), kv.view(torch.uint8), idx, 1.0, W, W, None, None)
+
+
+@pytest.mark.parametrize("impl", _impls(), ids=["extension", "ctypes"])
 def test_prefill_w_words_and_device(impl):
     q, kv, idx = _prefill_args()
     with pytest.raises(RuntimeError, match="8 pre-expanded"):

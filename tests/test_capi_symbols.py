@@ -37,10 +37,13 @@ def test_status_strings_and_argument_checks_need_no_gpu():
     assert b"NULL" in L.mxdsa_status_string(1)
     assert L.mxdsa_prefill_fwd(None) == 1          # MXDSA_ERR_NULL
     assert L.mxdsa_decode_fwd(None) == 1
-    p = capi.PrefillParams(s_q=3, s_kv=4, topk=64, q=16, kv=16, indices=16, out=16, max_logits=16, lse=16)
-    assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 2   # odd s_q -> MXDSA_ERR_SHAPE
-    p = capi.PrefillParams(s_q=4, s_kv=4, topk=96, q=16, kv=16, indices=16, out=16, max_logits=16, lse=16)
-    assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 2   # topk not a multiple of 64
+    p = capi.PrefillParams(s_q=0, s_kv=4, topk=64, q=16, kv=16, indices=16, out=16, max_logits=16, lse=16)
+    assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 2   # no query token -> MXDSA_ERR_SHAPE
+    p = capi.PrefillParams(s_q=4, s_kv=4, topk=0, q=16, kv=16, indices=16, out=16, max_logits=16, lse=16)
+    assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 2   # empty index rows
+    p = capi.PrefillParams(s_q=3, s_kv=4, topk=96, q=16, kv=16, indices=16, out=16, max_logits=16, lse=16,
+                           stride_q_token=64 * 528, stride_indices_pair=64)
+    assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 2   # index rows closer together than topk
     p = capi.PrefillParams(s_q=4, s_kv=4, topk=64, q=24, kv=16, indices=16, out=16, max_logits=16, lse=16,
                            stride_q_token=64 * 528, stride_indices_pair=64)
     assert L.mxdsa_prefill_fwd(ctypes.byref(p)) == 3   # q not 16-byte aligned -> MXDSA_ERR_ALIGN
