@@ -62,6 +62,14 @@
 #ifndef MXDSA_V_HINT
 #define MXDSA_V_HINT kEvictLast
 #endif
+// How many tiles ahead of the copies the index rows are asked into L2 (0: never)
+#ifndef MXDSA_INDEX_AHEAD
+#define MXDSA_INDEX_AHEAD 4
+#endif
+// 1: the epilogue warps write bf16 output through shared memory and tiled TMA stores; 0: 32-byte stores per lane
+#ifndef MXDSA_TMA_EPILOGUE
+#define MXDSA_TMA_EPILOGUE 1
+#endif
 #ifndef MXDSA_K_STAGES
 #define MXDSA_K_STAGES 2
 #define MXDSA_V_STAGES 2
@@ -145,6 +153,7 @@ struct TensorMaps {
     CUtensorMap q;        // 5-D {128 B, 64 heads, 4 chunks, tokens, requests}
     CUtensorMap kv;       // 2-D {512 B, rows}: data rows of the (main) KV store, row pitch 512 B; gather4 source for V
     CUtensorMap ekv;      // decode: the same over the extra pool
+    CUtensorMap out;      // 2-D {512 bf16, tokens x 64 heads} over the output; one store box = 32 columns of 32 rows
 };
 
 // One unit of work for a CTA pair: a query pair and a range of 64-key blocks of its key list.
@@ -165,6 +174,9 @@ struct __align__(1024) SmemPlan {
     uint8_t k[kKStages][4 * 64 * 128];             // [chunk][key of this CTA][128 B]
     uint8_t v[kVStages][2 * 128 * 128];            // [chunk of this CTA][key][128 B]
     uint8_t s[kSBufs][64 * 128];                        // [row][128 keys], 128-byte swizzle
+#if MXDSA_TMA_EPILOGUE
+    uint8_t o_stage[4][2][32 * 64];                // per epilogue warp: two tiles of 32 rows x 32 bf16 on their way out, 64-byte swizzle
+#endif
     __align__(16) uint16_t kvalid[kKStages][8];     // validity bits of the tile's keys, 16 per entry (K ring)
     __align__(128) uint32_t q_sf[64 * 4];          // scale rows for tcgen05.cp (64 rows x 16 B)
     __align__(128) uint32_t k_sf[kKStages][64 * 4];   // per K stage: K scale rows for tcgen05.cp, gathered by the producers with the rows
@@ -295,6 +307,21 @@ __device__ __forceinline__ int key_index(const AttnParams& p, const WorkItem& w,
         return pos < (extra ? p.extra_topk : p.topk) ? __ldg((extra ? w.erow : w.row) + pos) : -1;
     }
 }
+// Ask for the index lines of the two 64-key blocks blk, blk + 1 into L2: lane 0..3 takes 128-byte line lane % 2 of
+// block blk + lane / 2 (nothing where the block or the position does not exist).
+template <bool DECODE>
+__device__ __forceinline__ void prefetch_index_lines(const AttnParams& p, const WorkItem& w, int blk, int lane) {
+    const int b = blk + (lane >> 1);
+    if (b >= w.blk_end) return;
+    if constexpr (!DECODE) {
+        const int pos = b * 64 + (lane & 1) * 32;
+        if (pos < p.topk) prefetch_l2(w.row + pos);
+    } else {
+        const bool extra = b >= w.n_main_blocks;
+        const int pos = (extra ? b - w.n_main_blocks : b) * 64 + (lane & 1) * 32;
+        if (pos < (extra ? p.extra_topk : p.topk)) prefetch_l2((extra ? w.erow : w.row) + pos);
+    }
+}
 // Step 2: is the key attended, where are its 512 data bytes (nullptr = no row, the operand rows are
 // zero-filled) and its 16-byte scale slot.
 template <bool DECODE>
@@ -331,61 +358,31 @@ __device__ __forceinline__ const uint8_t* key_lookup(const AttnParams& p, const 
 }
 
 
-// Four consecutive positions j .. j+3 (j a multiple of 4) at once: one 16-byte load where the row allows it.
+// Row coordinate of one key in the 2-D view {512 B, rows} of its KV store (-1 = no row: the copy engine fills
+// zeros), from the key's raw index.
 template <bool DECODE>
-__device__ __forceinline__ int4 key_index4(const AttnParams& p, const WorkItem& w, int blk, int j) {
-    int4 r = make_int4(-1, -1, -1, -1);
-    if (blk >= w.blk_end) return r;
-    const int* row;
-    int pos, limit;
+__device__ __forceinline__ int key_row(const AttnParams& p, const WorkItem& w, int blk, int j, int idx) {
+    if (blk >= w.blk_end) return -1;
     if constexpr (!DECODE) {
-        row = w.row;
-        pos = blk * 64 + j;
-        limit = p.topk;
-    } else {
-        const bool extra = blk >= w.n_main_blocks;
-        row = extra ? w.erow : w.row;
-        pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
-        limit = extra ? p.extra_topk : p.topk;
-    }
-    if (pos + 3 < limit && (reinterpret_cast<unsigned long long>(row + pos) & 15u) == 0) {
-        r = __ldg(reinterpret_cast<const int4*>(row + pos));
-    } else {
-        if (pos < limit) r.x = __ldg(row + pos);
-        if (pos + 1 < limit) r.y = __ldg(row + pos + 1);
-        if (pos + 2 < limit) r.z = __ldg(row + pos + 2);
-        if (pos + 3 < limit) r.w = __ldg(row + pos + 3);
-    }
-    return r;
-}
-// Row coordinates of those four keys in the 2-D view {512 B, rows} of their KV store (-1 = no row), and the
-// tensor map of that store.
-template <bool DECODE>
-__device__ __forceinline__ const void* key_rows4(const AttnParams& p, const TensorMaps& maps, const WorkItem& w, int blk,
-                                                 int j, int4 ix, int (&r)[4]) {
-    const int id[4] = {ix.x, ix.y, ix.z, ix.w};
-    if constexpr (!DECODE) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) r[i] = (blk < w.blk_end && id[i] >= 0 && id[i] < p.s_kv) ? id[i] : -1;
-        return &maps.kv;
+        return (idx >= 0 && idx < p.s_kv) ? idx : -1;
     } else {
         const bool extra = blk >= w.n_main_blocks;
         const int pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
-        const int len = extra ? w.elen : w.len;
+        if (idx < 0 || idx >= (extra ? p.extra_pool_rows : p.pool_rows) || pos >= (extra ? w.elen : w.len)) return -1;
         const unsigned psz = extra ? p.extra_page_size : p.page_size;
         const unsigned rpb = extra ? p.extra_rows_per_block : p.rows_per_block;
         const int sh = extra ? p.extra_page_shift : p.page_shift;
-        const long long pool = extra ? p.extra_pool_rows : p.pool_rows;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const bool ok = blk < w.blk_end && id[i] >= 0 && id[i] < pool && pos + i < len;
-            const unsigned page = sh >= 0 ? (unsigned)id[i] >> sh : (unsigned)id[i] / psz;
-            const unsigned in_page = sh >= 0 ? (unsigned)id[i] & (psz - 1) : (unsigned)id[i] % psz;
-            r[i] = ok ? (int)(page * rpb + in_page) : -1;
-        }
-        // without an extra pool there is no second map: positions past the main list have no row anyway
-        return (extra && p.extra_topk > 0) ? &maps.ekv : &maps.kv;
+        const unsigned page = sh >= 0 ? (unsigned)idx >> sh : (unsigned)idx / psz;
+        const unsigned in_page = sh >= 0 ? (unsigned)idx & (psz - 1) : (unsigned)idx % psz;
+        return (int)(page * rpb + in_page);
     }
+}
+// The tensor map that the rows of 64-key block `blk` are gathered through.
+template <bool DECODE>
+__device__ __forceinline__ const void* key_map(const AttnParams& p, const TensorMaps& maps, const WorkItem& w, int blk) {
+    if constexpr (!DECODE) return &maps.kv;
+    // without an extra pool there is no second map: positions past the main list have no row anyway
+    else return (blk >= w.n_main_blocks && p.extra_topk > 0) ? &maps.ekv : &maps.kv;
 }
 
 // packed fp32 pairs (one instruction for two lanes of data)
@@ -622,6 +619,17 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             uint32_t kt = 0;
             int idx = ck.live ? key_index<DECODE>(p, ck.w, ck.w.blk_begin + 2 * ck.t + key / 64, key % 64) : -1;
             const uint32_t k_stage0 = smem_u32(sm.k[0]) + (lane / 8) * 8192;
+            // Where the key's row and scale slot are is worked out as soon as the tile's index is back, before the
+            // wait for a free stage: the wait then covers what is left of the index load's latency.
+            const uint8_t* cur = nullptr;
+            const uint8_t* slot = nullptr;
+            uint32_t vbits = 0;
+            auto resolve_tile = [&]() {
+                bool valid;
+                cur = key_resolve<DECODE>(p, ck.w, ck.w.blk_begin + 2 * ck.t + key / 64, key % 64, idx, valid, slot);
+                vbits = __ballot_sync(0xffffffffu, valid);
+            };
+            if (ck.live) resolve_tile();
 #pragma unroll 1
             while (ck.live) {
                 const uint32_t s = kt % kKStages;
@@ -629,13 +637,12 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     const uint32_t g = kt - kKStages;
                     MXDSA_WAIT(sm.bar_qk_done[g % kScStages], (g / kScStages) & 1, 10);
                 }
-                const uint8_t* cur;
-                const uint8_t* slot;
-                uint32_t vbits;
-                {
-                    bool valid;
-                    cur = key_resolve<DECODE>(p, ck.w, ck.w.blk_begin + 2 * ck.t + key / 64, key % 64, idx, valid, slot);
-                    vbits = __ballot_sync(0xffffffffu, valid);
+                // The index rows are read once, front to back, and never fit in L2 as a whole: four lanes of one
+                // warp ask for the 512 bytes that a tile further on will need, so that the index loads of all three
+                // roles that read them (these warps, the V producers, the stager) come back from L2, not from HBM.
+                if constexpr (MXDSA_INDEX_AHEAD > 0) {
+                    if (pw == 0 && cta == 0 && lane < 4 && ck.t + MXDSA_INDEX_AHEAD < ck.ntiles)
+                        prefetch_index_lines<DECODE>(p, ck.w, ck.w.blk_begin + 2 * (ck.t + MXDSA_INDEX_AHEAD), lane);
                 }
                 // the next tile's indices: the loads run while this tile's rows are issued
                 ck.advance();
@@ -662,6 +669,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     mbar_arrive(smem_u32(&sm.bar_k_landed[s]));
                 }
                 ++kt;
+                if (ck.live) resolve_tile();
             }
         } else {
             if constexpr (kRebalanceRegs) setmaxnreg_dec<kRegsGather>();
@@ -674,33 +682,52 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             // outside the tensor map, which the copy engine fills with zeros.  The bytes of both CTAs complete
             // on ONE barrier of CTA 0, where the PV issuer waits; nothing else needs to know that V has landed.
             const int pw = warp - 4;
-            const int j0 = 32 * pw + 4 * (lane & 7);     // first of this lane's four keys in the tile
+            const int jl = 32 * pw + lane;               // the key whose row this lane works out
+            const int j0 = 32 * pw + 4 * (lane & 7);     // first of the four keys this lane requests (lanes 0-7)
             TileCursor<DECODE, NT> cv(p);
             uint32_t vt = 0;
-            int4 ix = make_int4(-1, -1, -1, -1);
-            if (cv.live) ix = key_index4<DECODE>(p, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64);
             const uint32_t v_full0 = map_to_cta(smem_u32(&sm.bar_v_full[0]), 0);
             const uint32_t v_dst0 = smem_u32(sm.v[0]) + j0 * 128;
+            // Every lane turns ONE index into a row coordinate and the requesting lanes collect four of them: the
+            // warp's instructions are issued between those of six other warps of its scheduler, and a chain of
+            // address arithmetic four keys long per lane cost about 1000 cycles per tile.  The coordinates of a
+            // tile are worked out right after the requests of the tile before it, ahead of the wait for a free
+            // stage, and the index load they need is issued before those requests, which hold the warp long
+            // enough for it to come back.
+            int row = -1;
+            const void* map = &maps.kv;
+            auto locate = [&](int idx) {
+                const int blk = cv.w.blk_begin + 2 * cv.t + jl / 64;   // the same block for the warp's 32 keys
+                row = key_row<DECODE>(p, cv.w, blk, jl % 64, idx);
+                map = key_map<DECODE>(p, maps, cv.w, blk);
+            };
+            bool live = cv.live;
+            if (live) locate(key_index<DECODE>(p, cv.w, cv.w.blk_begin + 2 * cv.t + jl / 64, jl % 64));
 #pragma unroll 1
-            while (cv.live) {
+            while (live) {
                 const uint32_t s = vt % kVStages;
                 if (vt >= (uint32_t)kVStages) {   // stage s was last used by tile vt-3: its PV must be done
                     const uint32_t g = vt - kVStages;
                     MXDSA_WAIT(sm.bar_pv_done[g % kScStages], (g / kScStages) & 1, 11);
                 }
+                const void* map_cur = map;
                 int r[4];
-                const void* map = key_rows4<DECODE>(p, maps, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64, ix, r);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) r[i] = __shfl_sync(0xffffffffu, row, 4 * (lane & 7) + i);
                 cv.advance();
-                if (cv.live) ix = key_index4<DECODE>(p, cv.w, cv.w.blk_begin + 2 * cv.t + j0 / 64, j0 % 64);
+                live = cv.live;
+                int idx = -1;
+                if (live) idx = key_index<DECODE>(p, cv.w, cv.w.blk_begin + 2 * cv.t + jl / 64, jl % 64);
                 if (lane == 0) mbar_expect_tx_cluster(v_full0 + s * 8, 2 * 32 * 128);
                 __syncwarp();
                 if (lane < 8) {
                     const uint32_t dst = v_dst0 + s * 32768;
-                    tma_gather4_pair(dst, map, 256 * (int)cta, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
-                    tma_gather4_pair(dst + 16384, map, 256 * (int)cta + 128, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
+                    tma_gather4_pair(dst, map_cur, 256 * (int)cta, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
+                    tma_gather4_pair(dst + 16384, map_cur, 256 * (int)cta + 128, r[0], r[1], r[2], r[3], v_full0 + s * 8, MXDSA_V_HINT);
                 }
                 __syncwarp();
                 ++vt;
+                if (live) locate(idx);
             }
         }
     } else if (warp < 12) {
@@ -1174,6 +1201,42 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
             const int tok_idx = 2 * w.pair + (int)cta;
             const bool store = tok_idx < p.s_q;
             if (!DECODE || !w.split) {
+#if MXDSA_TMA_EPILOGUE
+                // 32 columns at a time: one load becomes 32 rows x 64 bytes of the warp's staging area (16-byte
+                // chunk c of row r sits at chunk c ^ ((r / 2) % 4), the 64-byte swizzle that the tensor map undoes
+                // and that keeps the eight lanes of a store phase on different banks), then one tiled store.  The
+                // area holds two such tiles, so that the copy engine reads one while the warp fills the other: an
+                // SM writes about 32 bytes per clock to global memory at best, and only with stores kept in flight
+                // (measured alone: 64 KB in 2470 cycles this way, 3330 with one tile, 3890 with 32-byte stores
+                // from the lanes).
+                const uint32_t stage0 = smem_u32(sm.o_stage[q4]);
+                const int out_row0 = (w.req * p.s_q + tok_idx) * kHeads + (q4 & 1) * 32;
+#pragma unroll 1
+                for (int c = 0; c < 256; c += 32) {
+                    float o[32];
+                    tmem_ld32(lane_addr + kColO + c, reinterpret_cast<uint32_t*>(o));
+                    tmem_wait_ld();
+                    const uint32_t tile = stage0 + ((c & 32) << 6);
+                    if (lane == 0) tma_store_wait_read<1>();   // the tile written two rounds ago has been read
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t u[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const __nv_bfloat162 v = __floats2bfloat162_rn(o[i + 2 * j] * oscale, o[i + 2 * j + 1] * oscale);
+                            u[j] = *reinterpret_cast<const uint32_t*>(&v);
+                        }
+                        st_shared_16B(tile + lane * 64 + (((i >> 3) ^ ((lane >> 1) & 3)) << 4), u[0], u[1], u[2], u[3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && store) {
+                        tma_store_2d(&maps.out, tile, half * 256 + c, out_row0);
+                        tma_store_commit();
+                    }
+                }
+#else
                 __nv_bfloat16* dst = p.out + (((long long)w.req * p.s_q + tok_idx) * kHeads + row) * kDim + half * 256;
 #pragma unroll 1
                 for (int c = 0; c < 256; c += 32) {
@@ -1197,6 +1260,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                         }
                     }
                 }
+#endif
             } else {
                 float* dst = p.o_accum + (((long long)w.split_idx * p.s_q + tok_idx) * kHeads + row) * kDim + half * 256;
 #pragma unroll 1
@@ -1226,6 +1290,10 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
 
 done:
     // ------------------------------------------------------------------ tear-down
+#if MXDSA_TMA_EPILOGUE
+    // stores still reading this CTA's shared memory must have done so before the CTA may end
+    if (warp >= 12 + 4 * G && lane == 0) tma_store_wait_read<0>();
+#endif
     // After a fault, softmax threads leave at different points; one extra arrival per leaving thread
     // completes the exchange barrier for those still parked on it (they fail their next wait and
     // follow).  In a normal exit the arrivals are harmless: nobody waits on that barrier any more.

@@ -110,6 +110,23 @@ int make_kv_map(CUtensorMap* map, const void* base, uint64_t rows) {
     return MXDSA_OK;
 }
 
+// 2-D map over the bf16 output viewed as {512 columns, tokens x 64 heads}: the epilogue stores boxes of
+// 32 columns x 32 rows out of 64-byte-swizzled staging tiles.
+int make_out_map(CUtensorMap* map, void* base, uint64_t tokens) {
+    cuuint64_t dims[2] = {MXDSA_DIM, tokens * MXDSA_HEADS};
+    cuuint64_t strides[1] = {MXDSA_DIM * 2};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t es[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, es,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tl_last_cuda_error = (int)r;
+        return MXDSA_ERR_CUDA;
+    }
+    return MXDSA_OK;
+}
+
 constexpr size_t kSmemBytes = sizeof(mxdsa::SmemPlan) + 1024;
 
 #ifndef MXDSA_GROUPS_PREFILL
@@ -415,6 +432,8 @@ int mxdsa_prefill_fwd(const mxdsa_prefill_params* p) {
     if (st != MXDSA_OK) return st;
     st = make_kv_map(&maps.kv, p->kv, (uint64_t)p->s_kv);
     if (st != MXDSA_OK) return st;
+    st = make_out_map(&maps.out, p->out, (uint64_t)p->s_q);
+    if (st != MXDSA_OK) return st;
 
     const int clusters = ap.num_pairs < d->sm_count / 2 ? ap.num_pairs : d->sm_count / 2;
     const dim3 grid(2 * clusters, 1, 1);
@@ -538,6 +557,9 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
                                                      (uint64_t)p->extra_page_block_size);
         if (st != MXDSA_OK) return st;
     }
+
+    st = make_out_map(&maps.out, p->out, (uint64_t)p->b * (uint64_t)p->s_q);
+    if (st != MXDSA_OK) return st;
 
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
     const dim3 grid(2 * ((p->s_q + 1) / 2), p->num_sm_parts, 1);

@@ -139,8 +139,27 @@ SM100_DEVICE void named_bar_sync(uint32_t id, uint32_t threads) {
 // ----------------------------------------------------------------------------------------------
 // TMA
 // ----------------------------------------------------------------------------------------------
+// Ask for the 128-byte line that holds `p` to be brought into L2; nothing is written back to the thread.
+SM100_DEVICE void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 SM100_DEVICE void prefetch_tensormap(const void* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+// Tiled store shared -> global of one 2-D box; the issuing thread groups its stores with tma_store_commit and
+// learns that their shared-memory source has been read (tma_store_wait_read) or that they are complete.
+SM100_DEVICE void tma_store_2d(const void* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :
+                 : "l"(map), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+SM100_DEVICE void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> SM100_DEVICE void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+SM100_DEVICE void st_shared_16B(uint32_t dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 static constexpr uint64_t kEvictFirst = 0x12F0000000000000ull;
 static constexpr uint64_t kEvictLast = 0x14F0000000000000ull;
