@@ -89,7 +89,10 @@ static constexpr int kTileKeys = 128;    // keys per tensor-core tile
 static constexpr int kKStages = MXDSA_K_STAGES;       // K ring depth (32 KB per stage and CTA); freed as soon as QK is done
 static constexpr int kVStages = MXDSA_V_STAGES;       // V ring depth (32 KB per stage and CTA); held until PV is done
 static constexpr int kSBufs = MXDSA_S_BUFS;      // S (quantised probabilities) ring: how far the softmax may run ahead of PV
-static constexpr int kScStages = 4;      // scale/validity ring depth; also the depth of the
+#ifndef MXDSA_SC_STAGES
+#define MXDSA_SC_STAGES 4
+#endif
+static constexpr int kScStages = MXDSA_SC_STAGES;      // scale/validity ring depth; also the depth of the
                                          // per-tile "QK done" / "PV done" barrier rings
 // registers per thread that a launch of 512 + 128 G threads gets (65536 / threads, rounded down to a multiple of 8)
 __host__ __device__ constexpr int launch_regs(int g) { return g == 2 ? 80 : 72; }

@@ -2,7 +2,8 @@
 # TEST INFRASTRUCTURE ONLY -- never part of the shipped library.
 #
 # Compiles the UNMODIFIED reference (dingirsu/MXDSA) from the sources where they lie
-# (location: MXDSA_REFERENCE_DIR, or the default set below) into oracle/_ref/mxdsa_ext.so.
+# (location: MXDSA_REFERENCE_DIR, or a checkout named "reference" beside this repository) into
+# oracle/_ref/mxdsa_ext.so.
 # Nothing is copied: nvcc/c++ read the reference's csrc/ tree in place and only object files
 # and the final .so are written under oracle/_ref/ (git-ignored).
 #
@@ -13,7 +14,7 @@
 # restricted to the sm_100 family target that a B200 needs.
 set -euo pipefail
 here="$(cd "$(dirname "$0")" && pwd)"
-ref="${MXDSA_REFERENCE_DIR:-/root/reference}"
+ref="${MXDSA_REFERENCE_DIR:-$here/../../reference}"
 out="$here/_ref"
 if [[ ! -d "$ref/csrc" ]]; then
     echo "reference sources not found at $ref; keeping any prebuilt $out" >&2

@@ -61,3 +61,30 @@ def check_against_oracle(out, ref):
     assert O.cosine(out, ref) >= 0.99999, ("cosine", O.cosine(out, ref))
     assert (d > OUT_MAX_ABS).mean() <= 2e-4, ("fraction beyond 2e-2", (d > OUT_MAX_ABS).mean())
     assert d.max() <= 0.5, ("max-abs", d.max())
+
+
+def decode_params(capi, c, dev_tensors, out, lse, meta, splits, parts, workspace):
+    """mxdsa_decode_params of the C ABI for a golden case `c` whose tensors already sit on the device."""
+    import ctypes as C
+
+    import torch
+    q, kv, idx, ekv, eidx = dev_tensors
+    w1 = (C.c_uint32 * 8)(*c["w1"])
+    w2 = (C.c_uint32 * 8)(*c["w2"])
+    have_extra = ekv is not None
+    return capi.DecodeParams(
+        b=q.shape[0], s_q=q.shape[1], topk=idx.shape[2], extra_topk=eidx.shape[2] if have_extra else 0,
+        sm_scale=c["sm_scale"], q=q.data_ptr(), stride_q_b=q.stride(0), stride_q_s=q.stride(1),
+        kv=kv.data_ptr(), num_blocks=kv.shape[0], page_block_size=kv.shape[1], stride_kv_block=kv.stride(0),
+        indices=idx.data_ptr(), stride_indices_b=idx.stride(0), stride_indices_s=idx.stride(1),
+        topk_length=None, attn_sink=None,
+        extra_kv=ekv.data_ptr() if have_extra else None, extra_num_blocks=ekv.shape[0] if have_extra else 0,
+        extra_page_block_size=ekv.shape[1] if have_extra else 0,
+        stride_extra_kv_block=ekv.stride(0) if have_extra else 0,
+        extra_indices=eidx.data_ptr() if have_extra else None,
+        stride_extra_indices_b=eidx.stride(0) if have_extra else 0,
+        stride_extra_indices_s=eidx.stride(1) if have_extra else 0, extra_topk_length=None, w1=w1, w2=w2,
+        out=out.data_ptr(), lse=lse.data_ptr(), sched_meta=meta.data_ptr(), num_splits=splits.data_ptr(),
+        num_sm_parts=parts, workspace=workspace.data_ptr() if workspace is not None else None,
+        workspace_bytes=workspace.numel() if workspace is not None else 0,
+        stream=torch.cuda.current_stream().cuda_stream)

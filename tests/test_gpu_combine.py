@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import cases
-from test_zz_no_alloc import _decode_params
+from helpers import decode_params
 
 pytestmark = pytest.mark.gpu
 
@@ -33,7 +33,7 @@ def test_combine_alone_matches_decode(name):
     out = torch.zeros((b, s_q, 64, 512), dtype=torch.bfloat16, device="cuda")
     lse = torch.zeros((b, s_q, 64), dtype=torch.float32, device="cuda")
     ws = torch.empty(need, dtype=torch.uint8, device="cuda")
-    p = _decode_params(capi, c, (q, kv, idx, ekv, eidx), out, lse, meta, splits, parts, ws)
+    p = decode_params(capi, c, (q, kv, idx, ekv, eidx), out, lse, meta, splits, parts, ws)
     capi.check(L.mxdsa_decode_fwd(C.byref(p)), "decode")
     capi.check(L.mxdsa_device_fault(stream), "fault")
     n_splits = (splits[1:] - splits[:-1]).cpu().numpy()

@@ -11,31 +11,9 @@ import pytest
 import torch
 
 import cases
+from helpers import decode_params
 
 pytestmark = pytest.mark.gpu
-
-
-def _decode_params(capi, c, dev_tensors, out, lse, meta, splits, parts, workspace):
-    q, kv, idx, ekv, eidx = dev_tensors
-    w1 = (C.c_uint32 * 8)(*c["w1"])
-    w2 = (C.c_uint32 * 8)(*c["w2"])
-    have_extra = ekv is not None
-    return capi.DecodeParams(
-        b=q.shape[0], s_q=q.shape[1], topk=idx.shape[2], extra_topk=eidx.shape[2] if have_extra else 0,
-        sm_scale=c["sm_scale"], q=q.data_ptr(), stride_q_b=q.stride(0), stride_q_s=q.stride(1),
-        kv=kv.data_ptr(), num_blocks=kv.shape[0], page_block_size=kv.shape[1], stride_kv_block=kv.stride(0),
-        indices=idx.data_ptr(), stride_indices_b=idx.stride(0), stride_indices_s=idx.stride(1),
-        topk_length=None, attn_sink=None,
-        extra_kv=ekv.data_ptr() if have_extra else None, extra_num_blocks=ekv.shape[0] if have_extra else 0,
-        extra_page_block_size=ekv.shape[1] if have_extra else 0,
-        stride_extra_kv_block=ekv.stride(0) if have_extra else 0,
-        extra_indices=eidx.data_ptr() if have_extra else None,
-        stride_extra_indices_b=eidx.stride(0) if have_extra else 0,
-        stride_extra_indices_s=eidx.stride(1) if have_extra else 0, extra_topk_length=None, w1=w1, w2=w2,
-        out=out.data_ptr(), lse=lse.data_ptr(), sched_meta=meta.data_ptr(), num_splits=splits.data_ptr(),
-        num_sm_parts=parts, workspace=workspace.data_ptr() if workspace is not None else None,
-        workspace_bytes=workspace.numel() if workspace is not None else 0,
-        stream=torch.cuda.current_stream().cuda_stream)
 
 
 @pytest.mark.parametrize("name", ["decode_main_only", "decode_mtp"])
@@ -61,7 +39,7 @@ def test_static_scratch_decode_matches_caller_scratch_decode(name):
         out = torch.full((b, s_q, 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
         lse = torch.full((b, s_q, 64), float("nan"), dtype=torch.float32, device="cuda")
         ws = None if static else torch.empty(need, dtype=torch.uint8, device="cuda")
-        p = _decode_params(capi, c, (q, kv, idx, ekv, eidx), out, lse, meta, splits, parts, ws)
+        p = decode_params(capi, c, (q, kv, idx, ekv, eidx), out, lse, meta, splits, parts, ws)
         fn = L.mxdsa_decode_fwd_static if static else L.mxdsa_decode_fwd
         capi.check(fn(C.byref(p)), "decode")
         capi.check(L.mxdsa_device_fault(torch.cuda.current_stream().cuda_stream), "fault")
