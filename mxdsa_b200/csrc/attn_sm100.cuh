@@ -526,6 +526,9 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
     const uint32_t cta = cluster_cta_rank();
 
     // ------------------------------------------------------------------ set-up
+    // decode: the combine grid that follows may be set up from now on (it waits for this grid's completion
+    // before it reads the partials)
+    if constexpr (DECODE) asm volatile("griddepcontrol.launch_dependents;");
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&sm.bar_q_landed), 1);
         mbar_init(smem_u32(&sm.bar_q_full), 2);

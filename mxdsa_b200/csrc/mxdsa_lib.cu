@@ -129,6 +129,9 @@ int make_out_map(CUtensorMap* map, void* base, uint64_t tokens) {
 
 constexpr size_t kSmemBytes = sizeof(mxdsa::SmemPlan) + 1024;
 
+#ifndef MXDSA_COMBINE_PDL
+#define MXDSA_COMBINE_PDL 1
+#endif
 #ifndef MXDSA_GROUPS_PREFILL
 #define MXDSA_GROUPS_PREFILL 3
 #endif
@@ -254,6 +257,10 @@ __global__ void __launch_bounds__(256) mxdsa_combine_kernel(int b, int s_q, int 
     if (!(begin_req < r || rec[2] == 0)) return;           // the request started in an earlier part
     const int s0 = num_splits[r], n = num_splits[r + 1] - s0;
     if (n <= 1) return;
+    // Launched as a programmatic dependent of the attention kernel (mxdsa_decode_fwd), this grid may start while
+    // that one is still running: everything above reads the schedule only, everything below reads the partials,
+    // which are complete and visible once the wait returns.  After a plain launch the wait returns at once.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const float* lse_in = lse_accum + ((long long)s0 * s_q + tok) * 64 + head;
     const long long lse_stride = (long long)s_q * 64;
     float mx = -CUDART_INF_F;
@@ -566,10 +573,22 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
     st = launch_pairs(mxdsa::mxdsa_attn_kernel<true, 64, MXDSA_GROUPS_DECODE>, MXDSA_GROUPS_DECODE, grid, stream, ap, maps);
     if (st != MXDSA_OK) return st;
     const dim3 cgrid(p->num_sm_parts * p->s_q, MXDSA_HEADS / 8, 1);
-    mxdsa_combine_kernel<<<cgrid, 256, 0, stream>>>(p->b, p->s_q, p->num_sm_parts, p->sched_meta, p->num_splits,
-                                                    o_accum, lse_accum, p->attn_sink,
-                                                    static_cast<__nv_bfloat16*>(p->out), p->lse);
-    MX_CUDA(cudaGetLastError());
+    // programmatic dependent launch: the combine grid is set up while the attention grid drains (the attention
+    // kernel releases its dependents as soon as it has started; the combine kernel waits before it reads)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = cgrid;
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = MXDSA_COMBINE_PDL;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MX_CUDA(cudaLaunchKernelEx(&cfg, mxdsa_combine_kernel, (int)p->b, (int)p->s_q, (int)p->num_sm_parts,
+                               (const int*)p->sched_meta, (const int*)p->num_splits, (const float*)o_accum,
+                               (const float*)lse_accum, (const float*)p->attn_sink,
+                               static_cast<__nv_bfloat16*>(p->out), (float*)p->lse));
     return MXDSA_OK;
 }
 
