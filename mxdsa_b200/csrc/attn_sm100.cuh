@@ -70,6 +70,9 @@
 #ifndef MXDSA_TMA_EPILOGUE
 #define MXDSA_TMA_EPILOGUE 1
 #endif
+#ifndef MXDSA_OUT_TILES
+#define MXDSA_OUT_TILES 2
+#endif
 #ifndef MXDSA_K_STAGES
 #define MXDSA_K_STAGES 2
 #define MXDSA_V_STAGES 2
@@ -88,6 +91,7 @@ static constexpr int kRowBytes = 528;
 static constexpr int kTileKeys = 128;    // keys per tensor-core tile
 static constexpr int kKStages = MXDSA_K_STAGES;       // K ring depth (32 KB per stage and CTA); freed as soon as QK is done
 static constexpr int kVStages = MXDSA_V_STAGES;       // V ring depth (32 KB per stage and CTA); held until PV is done
+static constexpr int kOutTiles = MXDSA_OUT_TILES;   // staging tiles per epilogue warp: stores in flight while the next tile is filled
 static constexpr int kSBufs = MXDSA_S_BUFS;      // S (quantised probabilities) ring: how far the softmax may run ahead of PV
 #ifndef MXDSA_SC_STAGES
 #define MXDSA_SC_STAGES 4
@@ -178,7 +182,7 @@ struct __align__(1024) SmemPlan {
     uint8_t v[kVStages][2 * 128 * 128];            // [chunk of this CTA][key][128 B]
     uint8_t s[kSBufs][64 * 128];                        // [row][128 keys], 128-byte swizzle
 #if MXDSA_TMA_EPILOGUE
-    uint8_t o_stage[4][2][32 * 64];                // per epilogue warp: two tiles of 32 rows x 32 bf16 on their way out, 64-byte swizzle
+    uint8_t o_stage[4][kOutTiles][32 * 64];        // per epilogue warp: tiles of 32 rows x 32 bf16 on their way out, 64-byte swizzle
 #endif
     __align__(16) uint16_t kvalid[kKStages][8];     // validity bits of the tile's keys, 16 per entry (K ring)
     __align__(128) uint32_t q_sf[64 * 4];          // scale rows for tcgen05.cp (64 rows x 16 B)
@@ -1189,9 +1193,17 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
         const int half = L / 64;
         const uint32_t lane_addr = tmem + (uint32_t(q4 * 32) << 16);
         const uint32_t o_empty0 = map_to_cta(smem_u32(&sm.bar_o_empty), 0);
+        // O is free for the next pair's first PV as soon as this warp has READ its last columns; the stores of
+        // those columns (which may have to wait for a staging tile) follow after the release.
+        auto release_o = [&]() {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(o_empty0);
+        };
         WorkIter<DECODE> it(p);
         WorkItem w;
         uint32_t gt = 0, gw = 0;
+        uint32_t round = 0;   // output rounds of this warp so far (staging tile = round % kOutTiles)
 #pragma unroll 1
         while (it.template next<NT>(w)) {
             const int ntiles = (w.blk_end - w.blk_begin + 1) / 2;
@@ -1211,7 +1223,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                 // 32 columns at a time: one load becomes 32 rows x 64 bytes of the warp's staging area (16-byte
                 // chunk c of row r sits at chunk c ^ ((r / 2) % 4), the 64-byte swizzle that the tensor map undoes
                 // and that keeps the eight lanes of a store phase on different banks), then one tiled store.  The
-                // area holds two such tiles, so that the copy engine reads one while the warp fills the other: an
+                // area holds kOutTiles such tiles, so that the copy engine reads some while the warp fills another: an
                 // SM writes about 32 bytes per clock to global memory at best, and only with stores kept in flight
                 // (measured alone: 64 KB in 2470 cycles this way, 3330 with one tile, 3890 with 32-byte stores
                 // from the lanes).
@@ -1222,8 +1234,10 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     float o[32];
                     tmem_ld32(lane_addr + kColO + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
-                    const uint32_t tile = stage0 + ((c & 32) << 6);
-                    if (lane == 0) tma_store_wait_read<1>();   // the tile written two rounds ago has been read
+                    if (c == 256 - 32) release_o();   // the last columns are in registers: the next pair's PV may go
+                    const uint32_t tile = stage0 + (round % kOutTiles) * 2048;   // tiles rotate across pairs too
+                    ++round;
+                    if (lane == 0) tma_store_wait_read<kOutTiles - 1>();   // the tile written kOutTiles rounds ago has been read
                     __syncwarp();
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -1237,8 +1251,8 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0 && store) {
-                        tma_store_2d(&maps.out, tile, half * 256 + c, out_row0);
+                    if (lane == 0) {   // a group per round, empty when nothing is stored, keeps "kOutTiles - 1 pending" exact
+                        if (store) tma_store_2d(&maps.out, tile, half * 256 + c, out_row0);
                         tma_store_commit();
                     }
                 }
@@ -1249,6 +1263,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     float o[32];
                     tmem_ld32(lane_addr + kColO + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
+                    if (c == 256 - 32) release_o();   // the last columns are in registers: the next pair's PV may go
                     if (store) {
                         // 32 columns -> 64 bytes of bf16: two 32-byte stores per lane (whole sectors; sixteen-byte
                         // stores from 32 lanes to 32 rows touch every sector twice and took twice as long)
@@ -1274,6 +1289,7 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     float o[32];
                     tmem_ld32(lane_addr + kColO + c, reinterpret_cast<uint32_t*>(o));
                     tmem_wait_ld();
+                    if (c == 256 - 32) release_o();   // the last columns are in registers: the next pair's PV may go
                     if (store) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
@@ -1287,9 +1303,6 @@ mxdsa_attn_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ 
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(o_empty0);
             ++gw;
         }
     }
