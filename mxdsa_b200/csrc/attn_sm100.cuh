@@ -18,10 +18,10 @@
 //               into the 128-byte-swizzled operand layout.  The same warps gather the 8 scale bytes of all 128
 //               keys of the tile into the row layout that tcgen05.cp wants, and vote the validity bits.
 //   warps 4-7   V producers: TMA gather4 (four rows x 128 bytes per request) of the 256-byte halves of all 128
-//               keys into the V ring; eight lanes per warp issue.  The bytes of both CTAs complete on one
-//               barrier of CTA 0.  (cp.async carrying V as well makes the K rows -- which the next QK waits
-//               for -- land late; the copy engine alone is the slower of the two paths, which is why K is not
-//               on it.)
+//               keys into the V ring; every lane works out one key's row coordinate, eight lanes per warp
+//               collect four each and issue.  The bytes of both CTAs complete on one barrier of CTA 0.
+//               (cp.async carrying V as well makes the K rows -- which the next QK waits for -- land late; the
+//               copy engine alone is the slower of the two paths, which is why K is not on it.)
 //   warp 8      CTA 0: QK issuer for even tiles      (issuers run as converged warps, one elected lane
 //   warp 9      CTA 0: QK issuer for odd tiles        issues fully unrolled MMAs; each has its own P buffer
 //   warp 10     CTA 0: PV issuer                      and scale columns)
@@ -33,8 +33,9 @@
 //               half of its tile): P -> registers, running max with lazy rescale handed from group to group,
 //               exp2, token scale, per-32-key UE8M0 requantisation to E4M3 S (ring of three), O rescale.
 //               At the end of a pair the groups add up their row sums and hand 1/l to the epilogue warps.
-//   warps 24-27 epilogue: drain O (tensor memory -> bf16 `out`, or fp32 split partials) while the other
-//               warps are already working on the next pair; only that pair's first PV waits for the drain.
+//   warps 24-27 epilogue: drain O (tensor memory -> bf16 `out` through small staging tiles and tiled TMA
+//               stores, or fp32 split partials) while the other warps are already working on the next pair;
+//               only that pair's first PV waits, and only until the last columns have been read.
 //
 // Numerical contract (identical to the reference kernels, reference file:line in brackets)
 //   * keys are consumed in numerical tiles of NT = 128 (prefill, topk >= 512) or 64 keys
