@@ -154,7 +154,8 @@ struct AttnParams {
     float* o_accum;           // [splits][s_q][64][512]
     float* lse_accum;         // [splits][s_q][64]
     int page_shift, extra_page_shift;         // log2(page size) when it is a power of two, else -1
-    long long pool_rows, extra_pool_rows;     // decode: keys in each pool (num_blocks * page_size); indices beyond are skipped
+    unsigned pool_rows32, extra_pool_rows32;  // decode: keys in each pool (num_blocks * page_size, at most 2^31); indices beyond are skipped
+    unsigned row_gap, extra_row_gap;          // rows_per_block - page_size: rows of the 512-byte view that a page's scale slots take
 };
 
 struct TensorMaps {
@@ -348,15 +349,22 @@ __device__ __forceinline__ const uint8_t* key_resolve(const AttnParams& p, const
         const bool extra = blk >= w.n_main_blocks;
         const int pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
         // an index outside the pool (stale or corrupt) is treated like -1: not attended, nothing dereferenced
-        valid = idx >= 0 && idx < (extra ? p.extra_pool_rows : p.pool_rows) && pos < (extra ? w.elen : w.len);
+        // (one unsigned compare: a negative index is a huge unsigned one)
+        valid = (unsigned)idx < (extra ? p.extra_pool_rows32 : p.pool_rows32) && pos < (extra ? w.elen : w.len);
         if (!valid) return nullptr;
         const unsigned psz = extra ? p.extra_page_size : p.page_size;
         const int sh = extra ? p.extra_page_shift : p.page_shift;   // pages are powers of two as a rule: no division then
-        const unsigned page = sh >= 0 ? (unsigned)idx >> sh : (unsigned)idx / psz;
-        const unsigned in_page = sh >= 0 ? (unsigned)idx & (psz - 1) : (unsigned)idx % psz;
+        unsigned page, in_page;
+        if (__builtin_expect(sh >= 0, 1)) {
+            page = (unsigned)idx >> sh;
+            in_page = (unsigned)idx & (psz - 1);
+        } else {
+            page = (unsigned)idx / psz;
+            in_page = (unsigned)idx - page * psz;
+        }
         const uint8_t* pg = (extra ? p.extra_kv : p.kv) + (long long)page * (extra ? p.extra_stride_block : p.stride_block);
-        slot = pg + (long long)psz * kDim + (long long)in_page * 16;
-        return pg + (long long)in_page * kDim;
+        slot = pg + psz * kDim + in_page * 16;
+        return pg + in_page * kDim;
     }
 }
 template <bool DECODE>
@@ -376,13 +384,13 @@ __device__ __forceinline__ int key_row(const AttnParams& p, const WorkItem& w, i
     } else {
         const bool extra = blk >= w.n_main_blocks;
         const int pos = (extra ? blk - w.n_main_blocks : blk) * 64 + j;
-        if (idx < 0 || idx >= (extra ? p.extra_pool_rows : p.pool_rows) || pos >= (extra ? w.elen : w.len)) return -1;
-        const unsigned psz = extra ? p.extra_page_size : p.page_size;
-        const unsigned rpb = extra ? p.extra_rows_per_block : p.rows_per_block;
+        if ((unsigned)idx >= (extra ? p.extra_pool_rows32 : p.pool_rows32) || pos >= (extra ? w.elen : w.len)) return -1;
+        // row = page * rows_per_block + slot in page = idx + page * (rows_per_block - page_size)
         const int sh = extra ? p.extra_page_shift : p.page_shift;
-        const unsigned page = sh >= 0 ? (unsigned)idx >> sh : (unsigned)idx / psz;
-        const unsigned in_page = sh >= 0 ? (unsigned)idx & (psz - 1) : (unsigned)idx % psz;
-        return (int)(page * rpb + in_page);
+        const unsigned gap = extra ? p.extra_row_gap : p.row_gap;
+        const unsigned page = __builtin_expect(sh >= 0, 1) ? (unsigned)idx >> sh
+                                                           : (unsigned)idx / (unsigned)(extra ? p.extra_page_size : p.page_size);
+        return (int)((unsigned)idx + page * gap);
     }
 }
 // The tensor map that the rows of 64-key block `blk` are gathered through.

@@ -543,8 +543,14 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
     auto log2_exact = [](int v) { int s = 0; while ((1 << s) < v) ++s; return (1 << s) == v ? s : -1; };
     ap.page_shift = log2_exact(p->page_block_size);
     ap.extra_page_shift = has_extra ? log2_exact(p->extra_page_block_size) : -1;
-    ap.pool_rows = (long long)p->num_blocks * p->page_block_size;
-    ap.extra_pool_rows = has_extra ? (long long)p->extra_num_blocks * p->extra_page_block_size : 0;
+    auto rows32 = [](long long blocks, long long page) {
+        const long long r = blocks * page;
+        return (unsigned)(r > 0x80000000ll ? 0x80000000ll : r);   // indices are int32: nothing beyond 2^31 can be named
+    };
+    ap.pool_rows32 = rows32(p->num_blocks, p->page_block_size);
+    ap.extra_pool_rows32 = has_extra ? rows32(p->extra_num_blocks, p->extra_page_block_size) : 0u;
+    ap.row_gap = (unsigned)(ap.rows_per_block - p->page_block_size);
+    ap.extra_row_gap = has_extra ? (unsigned)(ap.extra_rows_per_block - p->extra_page_block_size) : 0u;
     ap.sched_meta = p->sched_meta;
     ap.num_splits = p->num_splits;
     ap.o_accum = o_accum;
