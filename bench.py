@@ -330,6 +330,11 @@ def decode_sweep(torch, M, ref, peaks, batches, extras):
             gbs = gathered / ours["ms"] / 1e6
             row = dict(b=b, extra_topk=extra, ours=ours, latency_us=ours["ms"] * 1e3, gathered_bytes=gathered, gbs=gbs,
                        frac_of_measured_hbm=gbs / peaks["hbm_gbs"])
+            # the opt-in operator without a combine pass (whole requests per part; one launch, no scratch)
+            wf = M.dual_mxfp8_sparse_decode_fwd_whole(q, kv, idx, None, None, None, None, ek, ei, None, 512, 512, sc, w1, w2)
+            whole = graph_latency(torch, lambda: M.dual_mxfp8_sparse_decode_fwd_whole(q, kv, idx, None, None, wf[2], wf[3], ek,
+                                                                                     ei, None, 512, 512, sc, w1, w2), timed=30)
+            row["whole_request_latency_us"] = whole["ms"] * 1e3
             if ref is not None:
                 rf = ref.dual_mxfp8_sparse_decode_fwd(q, kv, idx, None, None, None, None, ek, ei, None, 512, 512, sc,
                                                       list(w1), list(w2))

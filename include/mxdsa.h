@@ -176,6 +176,22 @@ typedef struct mxdsa_combine_params {
 } mxdsa_combine_params;
 int mxdsa_decode_combine(const mxdsa_combine_params* p);
 
+/* ------------------------------------------------------------------------------------------
+ * Decode without a combine pass (no counterpart in the reference, whose scheduler always divides
+ * requests between parts: csrc/split_kv/scheduler.cu:61-112).
+ *
+ * mxdsa_decode_sched_whole writes records of the same layout as mxdsa_decode_sched in which every
+ * request belongs to exactly one part (consecutive requests per part, balanced by their number of
+ * 64-key blocks; num_splits[i] = i).  With such a schedule the attention kernel writes every
+ * output itself: mxdsa_decode_fwd_nocombine launches it alone -- `workspace` is ignored, nothing
+ * is merged afterwards.  The price is balance: a part's load is a whole number of requests.
+ * Should the schedule handed to mxdsa_decode_fwd_nocombine divide a request after all, that
+ * request's output is incomplete and the device fault record is raised (mxdsa_device_fault).
+ * The records are also valid input for mxdsa_decode_fwd (its combine then finds nothing to do).
+ * ------------------------------------------------------------------------------------------ */
+int mxdsa_decode_sched_whole(const mxdsa_sched_params* p);
+int mxdsa_decode_fwd_nocombine(const mxdsa_decode_params* p);
+
 /* Self-test of the kernels' bounded waits.  (No counterpart in the reference, whose kernels trap or spin.)
  * Launches a two-CTA kernel that waits -- with the attention kernel's own wait loops, limits turned down to
  * about a millisecond -- on a barrier nobody arrives on, gives up, raises the device fault record and leaves

@@ -58,11 +58,20 @@ def dual_mxfp8_sparse_decode_fwd(q, kv, indices, topk_length, attn_sink, tile_sc
                                               sm_scale, list(w1), list(w2))
 
 
+def dual_mxfp8_sparse_decode_fwd_whole(q, kv, indices, topk_length, attn_sink, tile_scheduler_metadata, num_splits,
+                                       extra_kv, extra_indices, extra_topk_length, d_qk, d_v, sm_scale, w1, w2):
+    """The decode operator without a combine pass: every request is given to one part, no scratch is allocated
+    (no counterpart in the reference; same arguments and return values as dual_mxfp8_sparse_decode_fwd)."""
+    return ext().dual_mxfp8_sparse_decode_fwd_whole(q, kv, indices, topk_length, attn_sink, tile_scheduler_metadata,
+                                                    num_splits, extra_kv, extra_indices, extra_topk_length, d_qk, d_v,
+                                                    sm_scale, list(w1), list(w2))
+
+
 def device_fault() -> None:
     """Synchronise the current stream; raise if a kernel abandoned one of its bounded waits."""
     ext().device_fault()
 
 
 __all__ = ["dual_mxfp8_head64_sparse_prefill_fwd", "dual_mxfp8_head64_sparse_prefill_fwd_ex",
-           "dual_mxfp8_sparse_decode_fwd", "device_fault", "ext", "api",
+           "dual_mxfp8_sparse_decode_fwd", "dual_mxfp8_sparse_decode_fwd_whole", "device_fault", "ext", "api",
            "capi", "packing"]

@@ -126,6 +126,38 @@ def dual_mxfp8_sparse_decode_fwd(q: torch.Tensor, kv: torch.Tensor, indices: tor
     Returns (out bf16 [b,s_q,64,512], lse f32 as a [b,64,s_q] view, tile_scheduler_metadata i32
     [num_sm_parts,8], num_splits i32 [b+1]); the last two are computed when passed as None and can
     be passed back in on later calls with the same shapes and lengths."""
+    return _decode(q, kv, indices, topk_length, attn_sink, tile_scheduler_metadata, num_splits, extra_kv,
+                   extra_indices, extra_topk_length, d_qk, d_v, sm_scale, w1, w2, whole=False)
+
+
+def dual_mxfp8_sparse_decode_fwd_whole(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
+                                 topk_length: Optional[torch.Tensor], attn_sink: Optional[torch.Tensor],
+                                 tile_scheduler_metadata: Optional[torch.Tensor],
+                                 num_splits: Optional[torch.Tensor], extra_kv: Optional[torch.Tensor],
+                                 extra_indices: Optional[torch.Tensor],
+                                 extra_topk_length: Optional[torch.Tensor], d_qk: int, d_v: int,
+                                 sm_scale: float, w1: Sequence[int], w2: Sequence[int]
+                                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The decode operator without a combine pass (no counterpart in the reference): the schedule gives every
+    request to one part (mxdsa_decode_sched_whole), the attention kernel writes all outputs itself, no scratch is
+    allocated.  Same arguments and return values; scheduling tensors passed back in must come from this function."""
+    return _decode(q, kv, indices, topk_length, attn_sink, tile_scheduler_metadata, num_splits, extra_kv,
+                   extra_indices, extra_topk_length, d_qk, d_v, sm_scale, w1, w2, whole=True)
+
+
+def _decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
+                                 topk_length: Optional[torch.Tensor], attn_sink: Optional[torch.Tensor],
+                                 tile_scheduler_metadata: Optional[torch.Tensor],
+                                 num_splits: Optional[torch.Tensor], extra_kv: Optional[torch.Tensor],
+                                 extra_indices: Optional[torch.Tensor],
+                                 extra_topk_length: Optional[torch.Tensor], d_qk: int, d_v: int,
+                                 sm_scale: float, w1: Sequence[int], w2: Sequence[int], whole: bool = False
+                                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Sparse MXFP8 decode attention with split-KV scheduling.  q [b,s_q,64,528], kv pages
+    [blocks,page,1,528], indices i32 [b,s_q,topk] (global slot ids); optional extra cache.
+    Returns (out bf16 [b,s_q,64,512], lse f32 as a [b,64,s_q] view, tile_scheduler_metadata i32
+    [num_sm_parts,8], num_splits i32 [b+1]); the last two are computed when passed as None and can
+    be passed back in on later calls with the same shapes and lengths."""
     _req(q.dim() == 4, "q must have 4 dimensions")
     _req(kv.dim() == 4, "kv must have 4 dimensions")
     _req(indices.dim() == 3, "indices must have 3 dimensions")
@@ -187,13 +219,13 @@ def dual_mxfp8_sparse_decode_fwd(q: torch.Tensor, kv: torch.Tensor, indices: tor
                                   extra_topk_length=_opt_ptr(extra_topk_length), num_sm_parts=parts,
                                   sched_meta=tile_scheduler_metadata.data_ptr(),
                                   num_splits=num_splits.data_ptr(), stream=stream)
-            capi.check(L.mxdsa_decode_sched(C.byref(sp)), "mxdsa_decode_sched")
+            capi.check((L.mxdsa_decode_sched_whole if whole else L.mxdsa_decode_sched)(C.byref(sp)), "mxdsa_decode_sched")
         _check_opt(tile_scheduler_metadata, "tile_scheduler_metadata", torch.int32, (parts, _SCHED_INTS))
         _req(num_splits is not None, "num_splits must be provided with tile_scheduler_metadata")
         _check_opt(num_splits, "num_splits", torch.int32, (b + 1,))
         _req(tile_scheduler_metadata.is_contiguous() and num_splits.is_contiguous(),
              "scheduling tensors must be contiguous")
-        ws_bytes = L.mxdsa_decode_workspace_bytes(b, s_q, parts)
+        ws_bytes = 0 if whole else L.mxdsa_decode_workspace_bytes(b, s_q, parts)
         workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=q.device)
         p = capi.DecodeParams(
             b=b, s_q=s_q, topk=topk, extra_topk=extra_topk, sm_scale=float(sm_scale),
@@ -209,8 +241,11 @@ def dual_mxfp8_sparse_decode_fwd(q: torch.Tensor, kv: torch.Tensor, indices: tor
             stride_extra_indices_s=extra_indices.stride(1) if have_extra else 0,
             extra_topk_length=_opt_ptr(extra_topk_length), w1=w1c, w2=w2c,
             out=out.data_ptr(), lse=lse.data_ptr(), sched_meta=tile_scheduler_metadata.data_ptr(),
-            num_splits=num_splits.data_ptr(), num_sm_parts=parts, workspace=workspace.data_ptr(),
+            num_splits=num_splits.data_ptr(), num_sm_parts=parts, workspace=None if whole else workspace.data_ptr(),
             workspace_bytes=ws_bytes, stream=stream)
+        if whole:
+            capi.check(L.mxdsa_decode_fwd_nocombine(C.byref(p)), "mxdsa_decode_fwd_nocombine")
+            return out, lse.transpose(1, 2), tile_scheduler_metadata, num_splits
         capi.check(L.mxdsa_decode_fwd(C.byref(p)), "mxdsa_decode_fwd")
         # the workspace is consumed by kernels already queued on this stream; record that use so
         # the caching allocator does not hand it to another stream before they finish

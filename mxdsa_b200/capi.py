@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libmxdsa.so")
 EXPORTS = (
     "mxdsa_status_string", "mxdsa_last_cuda_error", "mxdsa_device_fault", "mxdsa_prefill_fwd",
     "mxdsa_num_sm_parts", "mxdsa_decode_sched", "mxdsa_decode_workspace_bytes", "mxdsa_decode_fwd",
+    "mxdsa_decode_sched_whole", "mxdsa_decode_fwd_nocombine",
     "mxdsa_decode_fwd_static", "mxdsa_decode_combine", "mxdsa_pack_q", "mxdsa_pack_kv", "mxdsa_pack_last_cuda_error",
     "mxdsa_topk_select", "mxdsa_topk_last_cuda_error", "mxdsa_selftest_bounded_wait", "mxdsa_selftest_teardowns", "mxdsa_selftest_mma_rate",
 )
@@ -107,9 +108,11 @@ def lib() -> C.CDLL:
         L.mxdsa_prefill_fwd.argtypes = [C.POINTER(PrefillParams)]
         L.mxdsa_num_sm_parts.argtypes = [C.c_int, C.c_int]
         L.mxdsa_decode_sched.argtypes = [C.POINTER(SchedParams)]
+        L.mxdsa_decode_sched_whole.argtypes = [C.POINTER(SchedParams)]
         L.mxdsa_decode_workspace_bytes.restype = C.c_size_t
         L.mxdsa_decode_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
         L.mxdsa_decode_fwd.argtypes = [C.POINTER(DecodeParams)]
+        L.mxdsa_decode_fwd_nocombine.argtypes = [C.POINTER(DecodeParams)]
         L.mxdsa_decode_fwd_static.argtypes = [C.POINTER(DecodeParams)]
         L.mxdsa_decode_combine.argtypes = [C.POINTER(CombineParams)]
         L.mxdsa_pack_q.argtypes = [C.POINTER(PackQParams)]

@@ -273,6 +273,13 @@ template <bool DECODE> struct WorkIter {
             w.blk_end = r == meta[1] ? meta[3] : total;
             w.split = r == meta[0] ? meta[5] : (r == meta[1] ? meta[6] : 0);
             w.split_idx = __ldg(p.num_splits + r) + (r == meta[0] ? meta[4] : 0);
+            if (w.split && p.o_accum == nullptr) {
+                // a divided request in a launch without partials (decode without a combine pass needs a schedule of
+                // whole requests): flag it and write what this part has straight to `out` rather than through a
+                // null pointer
+                if (atomicCAS(&p.fault->flag, 0, 1) == 0) p.fault->where = 71;
+                w.split = 0;
+            }
             return true;
         }
     }

@@ -234,6 +234,49 @@ __global__ void __launch_bounds__(32) mxdsa_sched_kernel(int b, int topk, int ex
 }
 
 // ------------------------------------------------------------------------------------------
+// Whole-request scheduler: the same records, but no request is divided between parts, so that the attention
+// kernel writes every output itself and no combine pass is needed.  Part i takes the consecutive requests whose
+// midpoint (in 64-key blocks, prefix-summed) falls into the i-th of `parts` equal shares of the total; a part
+// without requests gets begin_req > end_req.  num_splits[i] = i.  The reference has no such schedule
+// (its scheduler, csrc/split_kv/scheduler.cu:61-112, always fills parts to an equal budget and splits).
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32) mxdsa_sched_whole_kernel(int b, int topk, int extra_topk, const int* topk_length,
+                                                              const int* extra_topk_length, int parts, int* meta,
+                                                              int* num_splits) {
+    extern __shared__ int nblk[];  // [b] blocks per request
+    int total = 0;
+    for (int i = threadIdx.x; i < b; i += 32) {
+        int len = topk_length ? topk_length[i] : topk;
+        len = len == 0 ? 1 : len;
+        if (extra_topk) len = (len + 63) / 64 * 64 + (extra_topk_length ? extra_topk_length[i] : extra_topk);
+        const int n = (max(len - 1, 0)) / 64 + 1;
+        nblk[i] = n;
+        total += n;
+    }
+    for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        int req = 0;
+        long long before = 0;   // blocks of the requests already given away
+        for (int i = 0; i < parts; ++i) {
+            const long long limit = (long long)total * (i + 1);   // midpoint * parts < limit  <=>  it lies in share i
+            const int first = req;
+            while (req < b && (i == parts - 1 || (2 * before + nblk[req]) * parts < 2 * limit)) before += nblk[req++];
+            int* rec = meta + 8 * i;
+            rec[0] = first;
+            rec[1] = req - 1;
+            rec[2] = 0;
+            rec[3] = req > first ? nblk[req - 1] : 0;
+            rec[4] = 0;
+            rec[5] = 0;
+            rec[6] = 0;
+            rec[7] = 0;
+        }
+    }
+    for (int i = threadIdx.x; i <= b; i += 32) num_splits[i] = i;
+}
+
+// ------------------------------------------------------------------------------------------
 // Split combine.  A request whose key blocks were divided between sm-parts has one fp32 partial
 // (O/l, log2 l + m) per split.  Every split request ends some part while continuing into the
 // next one; the part in which it STARTS (split 0) owns its merge.  One CTA per (part, token,
@@ -470,13 +513,27 @@ int mxdsa_decode_sched(const mxdsa_sched_params* p) {
     return MXDSA_OK;
 }
 
+// The whole-request schedule (see mxdsa_sched_whole_kernel): for mxdsa_decode_fwd_nocombine.
+int mxdsa_decode_sched_whole(const mxdsa_sched_params* p) {
+    if (p == nullptr || p->sched_meta == nullptr || p->num_splits == nullptr) return MXDSA_ERR_NULL;
+    if (p->b <= 0 || p->s_q <= 0 || p->topk <= 0 || p->extra_topk < 0 || p->num_sm_parts <= 0) return MXDSA_ERR_SHAPE;
+    const size_t smem = sizeof(int) * (2 * (size_t)p->b + 1);
+    if (smem > 200 * 1024) return MXDSA_ERR_SHAPE;
+    MX_CUDA(cudaFuncSetAttribute(mxdsa_sched_whole_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mxdsa_sched_whole_kernel<<<1, 32, smem, static_cast<cudaStream_t>(p->stream)>>>(
+        p->b, p->topk, p->extra_topk, p->topk_length, p->extra_topk_length, p->num_sm_parts, p->sched_meta,
+        p->num_splits);
+    MX_CUDA(cudaGetLastError());
+    return MXDSA_OK;
+}
+
 size_t mxdsa_decode_workspace_bytes(int b, int s_q, int num_sm_parts) {
     if (b <= 0 || s_q <= 0 || num_sm_parts <= 0) return 0;
     const size_t splits = (size_t)b + (size_t)num_sm_parts;
     return splits * s_q * MXDSA_HEADS * (MXDSA_DIM + 1) * sizeof(float);
 }
 
-int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
+static int decode_impl(const mxdsa_decode_params* p, bool combine) {
     if (p == nullptr || p->q == nullptr || p->kv == nullptr || p->indices == nullptr || p->out == nullptr ||
         p->lse == nullptr || p->sched_meta == nullptr || p->num_splits == nullptr)
         return MXDSA_ERR_NULL;
@@ -497,14 +554,16 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
         return MXDSA_ERR_ALIGN;
     if (p->stride_q_s < (int64_t)MXDSA_HEADS * MXDSA_ROW_BYTES) return MXDSA_ERR_SHAPE;
     const size_t need = mxdsa_decode_workspace_bytes(p->b, p->s_q, p->num_sm_parts);
-    if (p->workspace == nullptr || p->workspace_bytes < need || !aligned32(p->workspace)) return MXDSA_ERR_WORKSPACE;
+    if (combine && (p->workspace == nullptr || p->workspace_bytes < need || !aligned32(p->workspace)))
+        return MXDSA_ERR_WORKSPACE;
     DeviceInfo* d = nullptr;
     int st = device_info(&d);
     if (st != MXDSA_OK) return st;
 
+    // without a combine step there are no partials: the schedule must give every request to one part
     const size_t splits = (size_t)p->b + (size_t)p->num_sm_parts;
-    float* o_accum = static_cast<float*>(p->workspace);
-    float* lse_accum = o_accum + splits * p->s_q * MXDSA_HEADS * MXDSA_DIM;
+    float* o_accum = combine ? static_cast<float*>(p->workspace) : nullptr;
+    float* lse_accum = combine ? o_accum + splits * p->s_q * MXDSA_HEADS * MXDSA_DIM : nullptr;
 
     mxdsa::AttnParams ap;
     memset(&ap, 0, sizeof(ap));
@@ -578,6 +637,7 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
     const dim3 grid(2 * ((p->s_q + 1) / 2), p->num_sm_parts, 1);
     st = launch_pairs(mxdsa::mxdsa_attn_kernel<true, 64, MXDSA_GROUPS_DECODE>, MXDSA_GROUPS_DECODE, grid, stream, ap, maps);
     if (st != MXDSA_OK) return st;
+    if (!combine) return MXDSA_OK;
     const dim3 cgrid(p->num_sm_parts * p->s_q, MXDSA_HEADS / 8, 1);
     // programmatic dependent launch: the combine grid is set up while the attention grid drains (the attention
     // kernel releases its dependents as soon as it has started; the combine kernel waits before it reads)
@@ -597,6 +657,14 @@ int mxdsa_decode_fwd(const mxdsa_decode_params* p) {
                                static_cast<__nv_bfloat16*>(p->out), (float*)p->lse));
     return MXDSA_OK;
 }
+
+extern "C" int mxdsa_decode_fwd(const mxdsa_decode_params* p) { return decode_impl(p, true); }
+
+// Decode without a combine pass: attention only, no workspace.  The schedule must not divide any request between
+// parts (mxdsa_decode_sched_whole writes such a schedule); if it does, the kernel leaves the divided request's
+// output incomplete and raises the device fault record (code 71, reported by mxdsa_device_fault) instead of
+// writing partials that nobody would merge.
+extern "C" int mxdsa_decode_fwd_nocombine(const mxdsa_decode_params* p) { return decode_impl(p, false); }
 
 // ------------------------------------------------------------------------------------------
 // The combine step on its own: merges the split partials that an earlier mxdsa_decode_fwd (or any

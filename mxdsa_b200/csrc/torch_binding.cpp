@@ -136,11 +136,14 @@ std::vector<at::Tensor> prefill_fwd_ex(const at::Tensor& q, const at::Tensor& kv
     return prefill_impl(q, kv, indices, sm_scale, w1, w2, attn_sink, topk_length, true);
 }
 
-std::tuple<at::Tensor, at::Tensor, OptTensor, OptTensor> decode_fwd(
+// `whole` = false: the reference operator.  `whole` = true: the same operator with a schedule of whole requests
+// (mxdsa_decode_sched_whole), attention only -- no scratch, no combine pass; scheduling tensors passed in must come
+// from an earlier call of the same entry point.
+std::tuple<at::Tensor, at::Tensor, OptTensor, OptTensor> decode_impl(
     const at::Tensor& q, const at::Tensor& kv, const at::Tensor& indices, const OptTensor& topk_length,
     const OptTensor& attn_sink, OptTensor tile_scheduler_metadata, OptTensor num_splits, const OptTensor& extra_kv,
     const OptTensor& extra_indices, const OptTensor& extra_topk_length, int64_t d_qk, int64_t d_v, double sm_scale,
-    const std::vector<uint32_t>& w1, const std::vector<uint32_t>& w2) {
+    const std::vector<uint32_t>& w1, const std::vector<uint32_t>& w2, bool whole) {
     TORCH_CHECK(q.dim() == 4, "q must have 4 dimensions");
     TORCH_CHECK(kv.dim() == 4, "kv must have 4 dimensions");
     TORCH_CHECK(indices.dim() == 3, "indices must have 3 dimensions");
@@ -211,7 +214,7 @@ std::tuple<at::Tensor, at::Tensor, OptTensor, OptTensor> decode_fwd(
         sp.sched_meta = tile_scheduler_metadata->data_ptr<int32_t>();
         sp.num_splits = num_splits->data_ptr<int32_t>();
         sp.stream = stream.stream();
-        require_status(mxdsa_decode_sched(&sp), "mxdsa_decode_sched");
+        require_status(whole ? mxdsa_decode_sched_whole(&sp) : mxdsa_decode_sched(&sp), "mxdsa_decode_sched");
     }
     check_optional(tile_scheduler_metadata, "tile_scheduler_metadata", at::kInt, {parts, MXDSA_SCHED_META_INTS});
     TORCH_CHECK(num_splits.has_value(), "num_splits must be provided with tile_scheduler_metadata");
@@ -219,7 +222,8 @@ std::tuple<at::Tensor, at::Tensor, OptTensor, OptTensor> decode_fwd(
     TORCH_CHECK(tile_scheduler_metadata->is_contiguous() && num_splits->is_contiguous(),
                 "scheduling tensors must be contiguous");
 
-    const size_t ws_bytes = mxdsa_decode_workspace_bytes((int)b, (int)s_q, parts);
+    // whole-request schedules need no partials, hence no scratch
+    const size_t ws_bytes = whole ? 0 : mxdsa_decode_workspace_bytes((int)b, (int)s_q, parts);
     at::Tensor workspace = at::empty({(int64_t)ws_bytes}, opts.dtype(at::kByte));
     p.b = (int32_t)b;
     p.s_q = (int32_t)s_q;
@@ -253,13 +257,34 @@ std::tuple<at::Tensor, at::Tensor, OptTensor, OptTensor> decode_fwd(
     p.sched_meta = tile_scheduler_metadata->data_ptr<int32_t>();
     p.num_splits = num_splits->data_ptr<int32_t>();
     p.num_sm_parts = parts;
-    p.workspace = workspace.data_ptr();
+    p.workspace = whole ? nullptr : workspace.data_ptr();
     p.workspace_bytes = ws_bytes;
     p.stream = stream.stream();
-    require_status(mxdsa_decode_fwd(&p), "mxdsa_decode_fwd");
-    // the scratch is read by kernels queued on this stream after this function has returned
-    c10::cuda::CUDACachingAllocator::recordStream(workspace.storage().data_ptr(), stream);
+    if (whole) {
+        require_status(mxdsa_decode_fwd_nocombine(&p), "mxdsa_decode_fwd_nocombine");
+    } else {
+        require_status(mxdsa_decode_fwd(&p), "mxdsa_decode_fwd");
+        // the scratch is read by kernels queued on this stream after this function has returned
+        c10::cuda::CUDACachingAllocator::recordStream(workspace.storage().data_ptr(), stream);
+    }
     return {out, lse.transpose(1, 2), tile_scheduler_metadata, num_splits};
+}
+
+std::tuple<at::Tensor, at::Tensor, OptTensor, OptTensor> decode_fwd(
+    const at::Tensor& q, const at::Tensor& kv, const at::Tensor& indices, const OptTensor& topk_length,
+    const OptTensor& attn_sink, OptTensor tile_scheduler_metadata, OptTensor num_splits, const OptTensor& extra_kv,
+    const OptTensor& extra_indices, const OptTensor& extra_topk_length, int64_t d_qk, int64_t d_v, double sm_scale,
+    const std::vector<uint32_t>& w1, const std::vector<uint32_t>& w2) {
+    return decode_impl(q, kv, indices, topk_length, attn_sink, std::move(tile_scheduler_metadata), std::move(num_splits),
+                       extra_kv, extra_indices, extra_topk_length, d_qk, d_v, sm_scale, w1, w2, false);
+}
+std::tuple<at::Tensor, at::Tensor, OptTensor, OptTensor> decode_fwd_whole(
+    const at::Tensor& q, const at::Tensor& kv, const at::Tensor& indices, const OptTensor& topk_length,
+    const OptTensor& attn_sink, OptTensor tile_scheduler_metadata, OptTensor num_splits, const OptTensor& extra_kv,
+    const OptTensor& extra_indices, const OptTensor& extra_topk_length, int64_t d_qk, int64_t d_v, double sm_scale,
+    const std::vector<uint32_t>& w1, const std::vector<uint32_t>& w2) {
+    return decode_impl(q, kv, indices, topk_length, attn_sink, std::move(tile_scheduler_metadata), std::move(num_splits),
+                       extra_kv, extra_indices, extra_topk_length, d_qk, d_v, sm_scale, w1, w2, true);
 }
 
 void device_fault() {
@@ -272,6 +297,7 @@ static void define_module(pybind11::module_& m) {
     m.def("dual_mxfp8_head64_sparse_prefill_fwd", &prefill_fwd);
     m.def("dual_mxfp8_head64_sparse_prefill_fwd_ex", &prefill_fwd_ex);
     m.def("dual_mxfp8_sparse_decode_fwd", &decode_fwd);
+    m.def("dual_mxfp8_sparse_decode_fwd_whole", &decode_fwd_whole);
     m.def("device_fault", &device_fault);
 }
 

@@ -639,6 +639,36 @@ def sched_meta_ref(b: int, topk: int, extra_topk: int, num_sm_parts: int,
     return SchedMeta(meta, splits)
 
 
+def sched_whole_ref(b: int, topk: int, extra_topk: int, num_sm_parts: int,
+                    topk_length: Optional[np.ndarray] = None,
+                    extra_topk_length: Optional[np.ndarray] = None, block: int = 64) -> SchedMeta:
+    """Whole-request schedule (records of the layout of ``sched_meta_ref``; no request is divided, so decode needs
+    no combine pass).  The reference has no such schedule -- its scheduler (csrc/split_kv/scheduler.cu:61-112)
+    always fills parts to an equal budget and splits -- so the rule is this library's own, restated here for the
+    tests: part i takes the consecutive requests whose midpoint, in prefix-summed 64-key blocks, lies in the i-th
+    of ``num_sm_parts`` equal shares of the total (the last part takes what is left); num_splits[i] = i."""
+    nblk = []
+    for i in range(b):
+        s = int(topk_length[i]) if topk_length is not None else topk
+        if s == 0:
+            s = 1
+        if extra_topk:
+            s = -(-s // block) * block
+            s += int(extra_topk_length[i]) if extra_topk_length is not None else extra_topk
+        nblk.append(max(s - 1, 0) // block + 1)
+    total = sum(nblk)
+    meta = np.zeros((num_sm_parts, 8), dtype=np.int32)
+    req, before = 0, 0
+    for i in range(num_sm_parts):
+        first = req
+        while req < b and (i == num_sm_parts - 1 or (2 * before + nblk[req]) * num_sm_parts < 2 * total * (i + 1)):
+            before += nblk[req]
+            req += 1
+        meta[i] = [first, req - 1, 0, nblk[req - 1] if req > first else 0, 0, 0, 0, 0]
+    assert req == b
+    return SchedMeta(meta, np.arange(b + 1, dtype=np.int32))
+
+
 def combine_ref(lse_accum: np.ndarray, o_accum: np.ndarray, sink: Optional[np.ndarray]):
     """Merge of split partials (csrc/split_kv/combine.cu:66-125).  lse_accum [n,R] base-2,
     o_accum [n,R,512].  Returns (out [R,512] f64, lse [R] natural log, +inf when empty)."""
