@@ -137,6 +137,30 @@ def _big_prefill(s_q, s_kv, topk, seed, tail_invalid=0.0):
     return q, kv, idx.reshape(s_q // 2, 1, topk).contiguous(), w1, w2
 
 
+def test_prefill_full_size_addressing():
+    """sq = 65 536 query tokens (the headline size; Q alone is 2.2 GB): every byte offset beyond 2^31 must be
+    formed in 64 bits.  (The reference forms token x stride in 32 bits, csrc/attention/prefill_kernel.cuh:266-269,
+    and cannot run this size.)  The tail of the batch -- tokens past 63 551, where a 32-bit product wraps -- must
+    equal what a call on that slice alone returns, bit for bit, and the oracle on sampled pairs."""
+    import mxdsa_b200 as M
+    s_q, s_kv, topk = 65536, 16384, 128
+    q, kv, idx, w1, w2 = _big_prefill(s_q, s_kv, topk, seed=11)
+    sc = 512 ** -0.5
+    out, mxl, lse = M.dual_mxfp8_head64_sparse_prefill_fwd(q, kv, idx, sc, w1, w2, None, None)
+    M.device_fault()
+    lo = 63488
+    out_t, mxl_t, lse_t = M.dual_mxfp8_head64_sparse_prefill_fwd(q[lo:], kv, idx[lo // 2:], sc, w1, w2, None, None)
+    M.device_fault()
+    assert torch.equal(out[lo:].view(torch.int16), out_t.view(torch.int16))
+    assert torch.equal(lse[lo:], lse_t) and torch.equal(mxl[lo:], mxl_t)
+    pairs = [0, 31775, 31776, 32767]          # first pair, the two around the 2^31-byte mark, last pair
+    rows = sorted(sum(([2 * p, 2 * p + 1] for p in pairs), []))
+    ro, rm, rl = O.prefill_ref(q[rows].cpu().numpy(), kv.cpu().numpy(), idx[pairs].cpu().numpy(), sc, w1, w2,
+                               None, None, level=1)
+    check_against_oracle(out[rows].float().cpu().numpy(), ro)
+    assert np.abs(lse[rows].cpu().numpy() - rl).max() <= 1e-3
+
+
 def test_prefill_properties_at_headline_topk():
     """sq = 8192 query tokens against kv_len = 16384 with topk = 4096 (the headline tile count),
     10 % of every index row masked with -1 as in the multi-GPU configuration."""
